@@ -1,0 +1,335 @@
+// Host side of libleat_sampler.so: argument checks, the launch plan, and the extern "C" entry
+// points declared in include/leat_sampler.h.  Nothing here allocates device memory or synchronises
+// after leat_sampler_create().
+#include "../../include/leat_sampler.h"
+
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "sampler_kernels.cuh"
+
+using namespace leat;
+
+namespace {
+
+constexpr int kMaxSliceLen = 131072;  // bitmap of a slice: 16 KB
+constexpr int kSliceAlign = 128;
+constexpr int kMaxK = 1024;
+constexpr int kSpareCells = 4096;
+
+thread_local char g_cuda_error[256] = "";
+
+int cuda_failed(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return 0;
+  snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", what, cudaGetErrorString(e));
+  return 1;
+}
+
+int round_up(int x, int m) { return (x + m - 1) / m * m; }
+int next_pow2(int x) { int p = 1; while (p < x) p <<= 1; return p; }
+
+struct Layout {
+  size_t keys, count, best, vmin, ticket, flag, total;
+  int cells;
+};
+
+Layout layout_for(int max_rows, int max_vocab, int keep) {
+  Layout L;
+  L.cells = max_rows * ((max_vocab + kMaxSliceLen - 1) / kMaxSliceLen) + kSpareCells;
+  size_t at = 0;
+  auto take = [&](size_t bytes) { size_t here = at; at += (bytes + 255) / 256 * 256; return here; };
+  L.keys = take((size_t)L.cells * keep * 8);
+  L.count = take((size_t)L.cells * 4);
+  L.best = take((size_t)L.cells * 16);
+  L.vmin = take((size_t)L.cells * 4);
+  L.ticket = take((size_t)max_rows * 4);
+  L.flag = take((size_t)max_rows * 4);
+  L.total = at;
+  return L;
+}
+
+int keep_for(int k_max) { return round_up(k_max + 64, 64); }
+int cap_for(int keep) { return keep <= 512 ? 2048 : 4096; }
+
+}  // namespace
+
+struct leat_sampler {
+  int device, max_rows, max_vocab, k_max, keep, cap;
+  int tune_threads, tune_slices;
+  int sm_count;
+  int launches;
+  unsigned char* ws;
+  Layout L;
+};
+
+namespace {
+
+struct Plan {
+  int vec, threads, slices, slice_len, bm_words, ht_size, shared;
+};
+
+size_t shared_bytes(int cap, int bm_words, int ht_size) {
+  size_t stream = (size_t)bm_words * 4 + (size_t)ht_size * 8;
+  size_t finish = (size_t)cap * 8 + (size_t)(cap / 32) * 4;
+  return (size_t)cap * 8 + 1024 + 128 + (stream > finish ? stream : finish);
+}
+
+Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool has_history, int vec) {
+  Plan p;
+  p.vec = vec;
+  long long elems = (long long)rows * vocab;
+  p.threads = h->tune_threads ? h->tune_threads : (elems <= (4ll << 20) ? 256 : 512);
+  if (h->cap > EPT * p.threads) p.threads = h->cap / EPT;
+  int step = p.threads * vec * UNROLL;
+  int min_slices = (vocab + kMaxSliceLen - 1) / kMaxSliceLen;
+  int max_slices = (vocab + step - 1) / step;
+  if (max_slices < min_slices) max_slices = min_slices;
+  int per_sm = p.threads >= 512 ? 2 : 4;
+  int want = h->tune_slices ? h->tune_slices : (h->sm_count * per_sm * 4 + rows - 1) / rows;
+  int by_cells = h->L.cells / (rows > 0 ? rows : 1);
+  if (want > by_cells) want = by_cells;
+  if (want > max_slices) want = max_slices;
+  if (want < min_slices) want = min_slices;
+  if (want < 1) want = 1;
+  p.slice_len = round_up((vocab + want - 1) / want, kSliceAlign);
+  if (p.slice_len < 1) p.slice_len = kSliceAlign;
+  p.slices = (vocab + p.slice_len - 1) / p.slice_len;
+  if (p.slices < 1) p.slices = 1;
+  p.bm_words = has_history ? p.slice_len / 32 : 0;
+  p.ht_size = has_history ? next_pow2(history_cap * 2 < 64 ? 64 : history_cap * 2) : 0;
+  p.shared = (int)shared_bytes(h->cap, p.bm_words, p.ht_size);
+  return p;
+}
+
+bool aligned(const void* p, size_t a) { return ((uintptr_t)p % a) == 0; }
+
+int check_broadcast(const void* p, int n, int rows) { return !p || n == rows || n == 1; }
+
+int fill_params(const leat_sampler* h, const leat_sample_args* a, KParams& P) {
+  if (!h || !a) return LEAT_E_ARGUMENT;
+  if (a->rows < 0 || a->vocab <= 0) return LEAT_E_ARGUMENT;
+  if (a->rows > h->max_rows || a->vocab > h->max_vocab) return LEAT_E_CAPACITY;
+  if (!check_broadcast(a->options, a->options_rows, a->rows) ||
+      !check_broadcast(a->seed, a->seed_rows, a->rows) ||
+      !check_broadcast(a->position, a->position_rows, a->rows) ||
+      !check_broadcast(a->penalties, a->penalties_rows, a->rows))
+    return LEAT_E_ARGUMENT;
+  if (a->history && a->history_cap <= 0) return LEAT_E_ARGUMENT;
+  if (a->history && a->history_cap > 8192) return LEAT_E_CAPACITY;
+  if ((a->out_probs || a->out_prob_ids) && a->out_width <= 0) return LEAT_E_ARGUMENT;
+  memset(&P, 0, sizeof(P));
+  P.logits = a->logits; P.rows = a->rows; P.vocab = a->vocab; P.row_stride = a->row_stride;
+  P.vocab_total = a->vocab_total > 0 ? a->vocab_total : a->vocab;
+  P.options = a->options; P.options_rows = a->options_rows;
+  P.seed = a->seed; P.seed_rows = a->seed_rows;
+  P.position = a->position; P.position_rows = a->position_rows;
+  P.seen = a->seen; P.seen_stride = a->seen_stride;
+  P.history = a->history; P.history_len = a->history_len; P.history_cap = a->history ? a->history_cap : 0;
+  P.penalties = a->penalties; P.penalties_rows = a->penalties_rows;
+  P.uniform = a->uniform;
+  P.vocab_offset = a->vocab_offset; P.flags = a->flags;
+  P.out_ids = a->out_ids; P.out_greedy = a->out_greedy; P.out_cut = a->out_cut; P.out_kept = a->out_kept;
+  P.out_probs = a->out_probs; P.out_prob_ids = a->out_prob_ids; P.out_width = a->out_width;
+  P.status = a->status;
+  P.cap = h->cap; P.keep = h->keep; P.k_max = h->k_max;
+  P.ws_keys = reinterpret_cast<unsigned long long*>(h->ws + h->L.keys);
+  P.ws_count = reinterpret_cast<int*>(h->ws + h->L.count);
+  P.ws_best = reinterpret_cast<unsigned long long*>(h->ws + h->L.best);
+  P.ws_min = reinterpret_cast<float*>(h->ws + h->L.vmin);
+  P.ws_ticket = reinterpret_cast<unsigned*>(h->ws + h->L.ticket);
+  P.ws_flag = reinterpret_cast<int*>(h->ws + h->L.flag);
+  return LEAT_OK;
+}
+
+int pick_vec(const KParams& P) {
+  bool ok = P.vocab % 4 == 0 && P.row_stride % 4 == 0 && aligned(P.logits, 16);
+  if (P.seen) ok = ok && P.seen_stride % 4 == 0 && aligned(P.seen, 4);
+  return ok ? 4 : 1;
+}
+
+template <int VEC, bool PEN>
+int launch_one(const KParams& P, const Plan& plan, cudaStream_t stream) {
+  dim3 grid(plan.slices, P.rows);
+  sample_kernel<VEC, PEN><<<grid, plan.threads, plan.shared, stream>>>(P);
+  return cuda_failed(cudaGetLastError(), "sample_kernel launch") ? LEAT_E_CUDA : LEAT_OK;
+}
+
+int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
+  h->launches = 0;
+  if (P.rows == 0) return LEAT_OK;
+  int dev = -1;
+  if (cuda_failed(cudaGetDevice(&dev), "cudaGetDevice")) return LEAT_E_CUDA;
+  if (dev != h->device) return LEAT_E_DEVICE;
+  if (!P.logits || (!P.out_ids && !P.cand_count && !P.out_cut)) return LEAT_E_ARGUMENT;
+  const bool pen = P.seen != nullptr || P.history != nullptr;
+  const int vec = pick_vec(P);
+  Plan plan = make_plan(h, P.rows, P.vocab, P.history_cap, P.history != nullptr, vec);
+  P.slices = plan.slices; P.slice_len = plan.slice_len; P.bm_words = plan.bm_words; P.ht_size = plan.ht_size;
+  int rc;
+  if (vec == 4) rc = pen ? launch_one<4, true>(P, plan, stream) : launch_one<4, false>(P, plan, stream);
+  else rc = pen ? launch_one<1, true>(P, plan, stream) : launch_one<1, false>(P, plan, stream);
+  if (rc == LEAT_OK) h->launches += 1;
+  return rc;
+}
+
+template <typename K>
+int allow_shared(K kernel, int bytes) {
+  return cuda_failed(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes),
+                     "cudaFuncSetAttribute");
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t leat_sampler_workspace_bytes(int32_t max_rows, int32_t max_vocab, int32_t k_max) {
+  if (max_rows <= 0 || max_vocab <= 0 || k_max <= 0 || k_max > kMaxK) return 0;
+  return layout_for(max_rows, max_vocab, keep_for(k_max)).total;
+}
+
+int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t max_rows, int32_t max_vocab,
+                        int32_t k_max, leat_sampler_t** out) {
+  if (!workspace || !out || max_rows <= 0 || max_vocab <= 0 || k_max <= 0 || k_max > kMaxK)
+    return LEAT_E_ARGUMENT;
+  leat_sampler* h = new (std::nothrow) leat_sampler();
+  if (!h) return LEAT_E_ARGUMENT;
+  h->device = device; h->max_rows = max_rows; h->max_vocab = max_vocab; h->k_max = k_max;
+  h->keep = keep_for(k_max); h->cap = cap_for(h->keep);
+  h->tune_threads = 0; h->tune_slices = 0; h->launches = 0;
+  h->L = layout_for(max_rows, max_vocab, h->keep);
+  h->ws = static_cast<unsigned char*>(workspace);
+  if (bytes < h->L.total || !aligned(workspace, 256)) { delete h; return LEAT_E_WORKSPACE; }
+  int dev = -1;
+  if (cuda_failed(cudaGetDevice(&dev), "cudaGetDevice")) { delete h; return LEAT_E_CUDA; }
+  if (dev != device) { delete h; return LEAT_E_DEVICE; }
+  int sms = 0;
+  if (cuda_failed(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute")) {
+    delete h; return LEAT_E_CUDA;
+  }
+  h->sm_count = sms > 0 ? sms : 148;
+  const int most = (int)shared_bytes(h->cap, kMaxSliceLen / 32, 16384);
+  if (allow_shared(sample_kernel<4, true>, most) || allow_shared(sample_kernel<4, false>, most) ||
+      allow_shared(sample_kernel<1, true>, most) || allow_shared(sample_kernel<1, false>, most) ||
+      allow_shared(finish_candidates_kernel, most)) {
+    delete h; return LEAT_E_CUDA;
+  }
+  if (cuda_failed(cudaMemset(workspace, 0, h->L.total), "cudaMemset") ||
+      cuda_failed(cudaDeviceSynchronize(), "cudaDeviceSynchronize")) {
+    delete h; return LEAT_E_CUDA;
+  }
+  *out = h;
+  return LEAT_OK;
+}
+
+int leat_sampler_destroy(leat_sampler_t* handle) {
+  delete handle;
+  return LEAT_OK;
+}
+
+int leat_sampler_tune(leat_sampler_t* h, int32_t threads, int32_t slices) {
+  if (!h) return LEAT_E_ARGUMENT;
+  if (threads != 0 && threads != 128 && threads != 256 && threads != 512) return LEAT_E_ARGUMENT;
+  if (threads != 0 && h->cap > EPT * threads) return LEAT_E_ARGUMENT;
+  if (slices < 0) return LEAT_E_ARGUMENT;
+  h->tune_threads = threads; h->tune_slices = slices;
+  return LEAT_OK;
+}
+
+int leat_sampler_plan(const leat_sampler_t* h, int32_t rows, int32_t vocab, int32_t history_cap,
+                      int32_t* threads, int32_t* slices, int32_t* shared) {
+  if (!h || rows <= 0 || vocab <= 0) return LEAT_E_ARGUMENT;
+  Plan p = make_plan(h, rows, vocab, history_cap, history_cap > 0, vocab % 4 == 0 ? 4 : 1);
+  if (threads) *threads = p.threads;
+  if (slices) *slices = p.slices;
+  if (shared) *shared = p.shared;
+  return LEAT_OK;
+}
+
+int leat_sampler_last_launches(const leat_sampler_t* h) { return h ? h->launches : 0; }
+
+const char* leat_sampler_last_cuda_error(void) { return g_cuda_error; }
+
+int leat_sample(leat_sampler_t* h, const leat_sample_args* a, leat_stream_t stream) {
+  KParams P;
+  int rc = fill_params(h, a, P);
+  if (rc != LEAT_OK) return rc;
+  if (!a->out_ids) return LEAT_E_ARGUMENT;
+  return launch_sample(h, P, static_cast<cudaStream_t>(stream));
+}
+
+int leat_argmax(leat_sampler_t* h, const float* x, int32_t rows, int32_t vocab, int64_t row_stride,
+                int32_t* out, int32_t* status, leat_stream_t stream) {
+  leat_sample_args a;
+  memset(&a, 0, sizeof(a));
+  a.logits = x; a.rows = rows; a.vocab = vocab; a.row_stride = row_stride;
+  a.out_ids = out; a.status = status;
+  KParams P;
+  int rc = fill_params(h, &a, P);
+  if (rc != LEAT_OK) return rc;
+  if (!out) return LEAT_E_ARGUMENT;
+  P.force_greedy = 1;
+  return launch_sample(h, P, static_cast<cudaStream_t>(stream));
+}
+
+int leat_cutoff(leat_sampler_t* h, const float* scores, int32_t rows, int32_t vocab, int64_t row_stride,
+                const float* top_k, const float* top_p, const float* min_p, float* cut, int32_t* status,
+                leat_stream_t stream) {
+  if (!top_k || !top_p || !min_p || !cut) return LEAT_E_ARGUMENT;
+  leat_sample_args a;
+  memset(&a, 0, sizeof(a));
+  a.logits = scores; a.rows = rows; a.vocab = vocab; a.row_stride = row_stride;
+  a.out_cut = cut; a.status = status;
+  KParams P;
+  int rc = fill_params(h, &a, P);
+  if (rc != LEAT_OK) return rc;
+  P.opt_k = top_k; P.opt_p = top_p; P.opt_m = min_p;
+  return launch_sample(h, P, static_cast<cudaStream_t>(stream));
+}
+
+int leat_verify_draft(const int32_t* drafted, const int32_t* sampled, const int32_t* greedy, int32_t n,
+                      int32_t drafts, int32_t* accepted, int32_t* tokens, leat_stream_t stream) {
+  if (!sampled || !accepted || !tokens || n < 0 || drafts < 0 || (drafts > 0 && !drafted)) return LEAT_E_ARGUMENT;
+  if (n == 0) return LEAT_OK;
+  verify_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(drafted, sampled, greedy, n,
+                                                                                drafts, accepted, tokens);
+  return cuda_failed(cudaGetLastError(), "verify_kernel launch") ? LEAT_E_CUDA : LEAT_OK;
+}
+
+int leat_topk_local(leat_sampler_t* h, const leat_sample_args* a, float* cand_value, int32_t* cand_id,
+                    int32_t* cand_count, uint64_t* best, int32_t cap, leat_stream_t stream) {
+  if (!cand_value || !cand_id || !cand_count || !best || cap <= 0) return LEAT_E_ARGUMENT;
+  KParams P;
+  int rc = fill_params(h, a, P);
+  if (rc != LEAT_OK) return rc;
+  P.cand_value = cand_value; P.cand_id = cand_id; P.cand_count = cand_count;
+  P.cand_best = reinterpret_cast<unsigned long long*>(best); P.cand_cap = cap;
+  return launch_sample(h, P, static_cast<cudaStream_t>(stream));
+}
+
+int leat_sample_from_candidates(leat_sampler_t* h, const leat_sample_args* a, const float* cand_value,
+                                const int32_t* cand_id, const int32_t* cand_count, const uint64_t* best,
+                                int32_t parts, int32_t cap, leat_stream_t stream) {
+  if (!cand_value || !cand_id || !cand_count || !best || cap <= 0 || parts <= 0) return LEAT_E_ARGUMENT;
+  KParams P;
+  int rc = fill_params(h, a, P);
+  if (rc != LEAT_OK) return rc;
+  if (!a->out_ids) return LEAT_E_ARGUMENT;
+  h->launches = 0;
+  if (P.rows == 0) return LEAT_OK;
+  int dev = -1;
+  if (cuda_failed(cudaGetDevice(&dev), "cudaGetDevice")) return LEAT_E_CUDA;
+  if (dev != h->device) return LEAT_E_DEVICE;
+  P.g_value = cand_value; P.g_id = cand_id; P.g_count = cand_count;
+  P.g_best = reinterpret_cast<const unsigned long long*>(best); P.g_parts = parts; P.cand_cap = cap;
+  const int threads = h->cap > EPT * 256 ? h->cap / EPT : 256;
+  const int shared = (int)shared_bytes(h->cap, 0, 0);
+  finish_candidates_kernel<<<P.rows, threads, shared, static_cast<cudaStream_t>(stream)>>>(P);
+  if (cuda_failed(cudaGetLastError(), "finish_candidates_kernel launch")) return LEAT_E_CUDA;
+  h->launches = 1;
+  return LEAT_OK;
+}
+
+}  // extern "C"
