@@ -71,10 +71,10 @@ struct Plan {
   int vec, threads, slices, slice_len, bm_words, ht_size, shared;
 };
 
-size_t shared_bytes(int cap, int bm_words, int ht_size) {
+size_t shared_bytes(int cap, int keep, int bm_words, int ht_size) {
   size_t stream = (size_t)bm_words * 4 + (size_t)ht_size * 8;
   size_t finish = (size_t)cap * 8 + (size_t)(cap / 32) * 4;
-  return (size_t)cap * 8 + 1024 + 128 + (stream > finish ? stream : finish);
+  return (size_t)cap * 8 + (size_t)keep * 8 + (size_t)(BINS + 32) * 4 + 128 + (stream > finish ? stream : finish);
 }
 
 Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool has_history, int vec) {
@@ -82,7 +82,6 @@ Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool
   p.vec = vec;
   long long elems = (long long)rows * vocab;
   p.threads = h->tune_threads ? h->tune_threads : (elems <= (4ll << 20) ? 256 : 512);
-  if (h->cap > EPT * p.threads) p.threads = h->cap / EPT;
   int step = p.threads * vec * UNROLL;
   int min_slices = (vocab + kMaxSliceLen - 1) / kMaxSliceLen;
   int max_slices = (vocab + step - 1) / step;
@@ -100,7 +99,7 @@ Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool
   if (p.slices < 1) p.slices = 1;
   p.bm_words = has_history ? p.slice_len / 32 : 0;
   p.ht_size = has_history ? next_pow2(history_cap * 2 < 64 ? 64 : history_cap * 2) : 0;
-  p.shared = (int)shared_bytes(h->cap, p.bm_words, p.ht_size);
+  p.shared = (int)shared_bytes(h->cap, h->keep, p.bm_words, p.ht_size);
   return p;
 }
 
@@ -210,7 +209,7 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
     delete h; return LEAT_E_CUDA;
   }
   h->sm_count = sms > 0 ? sms : 148;
-  const int most = (int)shared_bytes(h->cap, kMaxSliceLen / 32, 16384);
+  const int most = (int)shared_bytes(h->cap, h->keep, kMaxSliceLen / 32, 16384);
   if (allow_shared(sample_kernel<4, true>, most) || allow_shared(sample_kernel<4, false>, most) ||
       allow_shared(sample_kernel<1, true>, most) || allow_shared(sample_kernel<1, false>, most) ||
       allow_shared(finish_candidates_kernel, most)) {
@@ -232,7 +231,6 @@ int leat_sampler_destroy(leat_sampler_t* handle) {
 int leat_sampler_tune(leat_sampler_t* h, int32_t threads, int32_t slices) {
   if (!h) return LEAT_E_ARGUMENT;
   if (threads != 0 && threads != 128 && threads != 256 && threads != 512) return LEAT_E_ARGUMENT;
-  if (threads != 0 && h->cap > EPT * threads) return LEAT_E_ARGUMENT;
   if (slices < 0) return LEAT_E_ARGUMENT;
   h->tune_threads = threads; h->tune_slices = slices;
   return LEAT_OK;
@@ -324,8 +322,8 @@ int leat_sample_from_candidates(leat_sampler_t* h, const leat_sample_args* a, co
   if (dev != h->device) return LEAT_E_DEVICE;
   P.g_value = cand_value; P.g_id = cand_id; P.g_count = cand_count;
   P.g_best = reinterpret_cast<const unsigned long long*>(best); P.g_parts = parts; P.cand_cap = cap;
-  const int threads = h->cap > EPT * 256 ? h->cap / EPT : 256;
-  const int shared = (int)shared_bytes(h->cap, 0, 0);
+  const int threads = 512;
+  const int shared = (int)shared_bytes(h->cap, h->keep, 0, 0);
   finish_candidates_kernel<<<P.rows, threads, shared, static_cast<cudaStream_t>(stream)>>>(P);
   if (cuda_failed(cudaGetLastError(), "finish_candidates_kernel launch")) return LEAT_E_CUDA;
   h->launches = 1;

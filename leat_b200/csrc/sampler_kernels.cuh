@@ -2,15 +2,19 @@
 //
 // One launch samples every row.  A row of logits is cut into `slices` contiguous pieces, one
 // thread block each (grid = slices x rows).  A block streams its piece from HBM exactly once with
-// 128-bit loads, applies the penalties (history ids are scattered into a shared-memory bitmap and a
-// small hash table of counts first) and the temperature, and keeps the piece's candidates -- every
-// score at or above the piece's k-th largest -- in a shared-memory buffer guarded by a running
-// threshold: an element is appended only if it beats the threshold, and the buffer is reduced by
-// an in-register radix select whenever it fills.  Each block publishes its candidates to the
-// handle's workspace and takes a ticket; the block that draws the last ticket of a row merges the
-// row's candidates with the same select, sorts the few survivors, and finishes the row: top-p inside
-// the top-k by a block scan, the min-p floor, the cut, probabilities, and the draw.  No block waits
-// for another.
+// 128-bit loads.  History ids are first scattered into a shared-memory bitmap and a small hash
+// table of counts, so penalties cost one shared-memory word per four logits.  The hot loop only
+// compares raw logits against a conservative threshold; the few that pass (and the penalised ones)
+// take an exact path that applies penalties and temperature and appends (score, id) to a
+// shared-memory candidate buffer.  When the buffer fills, the block rebuilds it around the exact
+// k-th largest score by a radix select and raises the threshold.  The block meets at one barrier
+// per streaming step (the next step's loads are already in flight), which is where it learns
+// whether any warp ran out of buffer.
+//
+// Each block publishes its candidates to the handle's workspace and takes a ticket; the block
+// that draws a row's last ticket merges the row's candidates with the same select, sorts the few
+// survivors, and finishes the row: top-p inside the top-k by a block scan, the min-p floor, the
+// cut, probabilities, and the draw.  No block ever waits for another.
 //
 // Semantics follow leat/sampler.py:31-73 and leat/ops.py:496-529 (the exact, sort-based cut).
 #pragma once
@@ -19,16 +23,18 @@
 namespace leat {
 
 enum RowMode : int {
-  M_ARGMAX_L = 0,   // greedy: first argmax of the penalised logits
-  M_ARGMAX_G = 1,   // no cut set, hashed draw: first argmax of score + gumbel over the whole row
-  M_SELECT_K = 2,   // candidates = scores >= the k-th largest
+  M_ARGMAX_L = 0,     // greedy: first argmax of the penalised logits
+  M_ARGMAX_G = 1,     // no cut set, hashed draw: first argmax of score + gumbel over the whole row
+  M_SELECT_K = 2,     // candidates = scores >= the k-th largest
   M_SELECT_MINP = 3,  // candidates = scores >= top + log(min_p)
-  M_GENERAL = 4     // needs the multi-pass kernel
+  M_GENERAL = 4       // needs the multi-pass kernel
 };
 
-constexpr int EPT = 16;        // buffer entries a thread holds in registers while the buffer is rebuilt
-constexpr int UNROLL = 4;      // vectors per thread per streaming step
+constexpr int UNROLL = 4;  // vectors per thread per streaming step
+constexpr int BINS = 2048;  // buckets of one select step
 constexpr int HASH_EMPTY = -1;
+constexpr int NO_ID = 0x7FFFFFFF;
+constexpr float GUMBEL_MAX = 17.0f;  // above -log(-log(1 - 2^-24)) = 16.64
 
 struct KParams {
   const float* logits; int rows; int vocab; long long row_stride; int vocab_total;
@@ -51,30 +57,40 @@ struct KParams {
   // workspace
   unsigned long long* ws_keys;  // (rows, slices, keep)
   int* ws_count;                // (rows, slices): candidates published, -1 = could not reduce
-  unsigned long long* ws_best;  // (rows, slices): greedy / whole-row argmax key
+  unsigned long long* ws_best;  // (rows, slices, 2): greedy key, whole-row argmax key
   float* ws_min;                // (rows, slices): smallest score of the slice
   unsigned* ws_ticket;          // (rows)
   int* ws_flag;                 // (rows): 1 = the row needs the multi-pass kernel
 };
 
 struct RowCfg {
-  float T, k, p, m, rinv, rep, pres, freq, u, logm;
-  int mode, k_eff, has_cut, greedy, track;
+  float T, k, p, m, rinv, tf, rep, pres, freq, u, logm;
+  int mode, k_eff, has_cut, greedy, track, divide;
   uint32_t rkey;
 };
 
 struct Shared {
-  int n;                 // entries appended to the buffer (may exceed cap until the next rebuild)
-  float tau;             // running threshold on scores
-  int overflow;          // the slice / row cannot be reduced to `keep` candidates
-  int sel_bin, sel_rem;
-  unsigned diff, vmax;
+  int n;         // entries in the buffer (may run past cap until the next rebuild)
+  int m;         // entries staged by a rebuild
+  float tau;     // running threshold on scores
+  int overflow;  // the slice / row cannot be reduced to `keep` candidates
+  int sel_bin, sel_above, sel_count;
+  unsigned vmin, vmax;
   int is_last;
   unsigned long long best;   // block max of an argmax key
   unsigned long long gbest;  // block max of the greedy key
   unsigned smin;             // block min of score bits (ord32)
   int jstar, ns, pick;
-  float kept, total, cut;
+};
+
+// what the candidate buffer needs, by value in registers
+struct Ctx {
+  unsigned long long* buf;
+  unsigned long long* stage;
+  unsigned* hist;
+  Shared* sm;
+  int cap, keep, mode, k;
+  float logm;
 };
 
 __device__ __forceinline__ float penalised(float l, int count, const RowCfg& rc) {
@@ -83,8 +99,15 @@ __device__ __forceinline__ float penalised(float l, int count, const RowCfg& rc)
   return r - off;
 }
 
-__device__ __forceinline__ float scaled(float l, const RowCfg& rc, bool divide, float tfloor) {
-  return divide ? l / tfloor : l * rc.rinv;
+__device__ __forceinline__ float scaled(float l, const RowCfg& rc) {
+  return rc.divide ? l / rc.tf : l * rc.rinv;
+}
+
+// a raw logit below this cannot reach score `tau` (conservative: the exact test follows)
+__device__ __forceinline__ float logit_floor(float tau, float tf) {
+  if (!(tau > neg_inf())) return neg_inf();
+  float g = tau * tf;
+  return g - fabsf(g) * 9.5367431640625e-07f - 1e-37f;
 }
 
 __device__ inline RowCfg row_config(const KParams& P, int b) {
@@ -102,8 +125,9 @@ __device__ inline RowCfg row_config(const KParams& P, int b) {
     const float* q = P.penalties + (size_t)(P.penalties_rows == 1 ? 0 : b) * 3;
     rc.rep = q[0]; rc.pres = q[1]; rc.freq = q[2];
   }
-  float tf = fmaxf(rc.T, 1e-6f);
-  rc.rinv = 1.0f / tf;
+  rc.tf = fmaxf(rc.T, 1e-6f);
+  rc.rinv = 1.0f / rc.tf;
+  rc.divide = (P.flags & 1u) ? 1 : 0;
   rc.u = P.uniform ? P.uniform[b] : 0.0f;
   rc.logm = log_ref(rc.m);
   rc.greedy = (P.force_greedy || !(rc.T > 0.0f)) ? 1 : 0;
@@ -125,133 +149,138 @@ __device__ inline RowCfg row_config(const KParams& P, int b) {
 
 // ---- candidate buffer -------------------------------------------------------------------------
 
-// Appends `key` from every thread whose `want` is set; returns false for a thread whose entry did
-// not fit (the buffer must then be rebuilt and the append retried).  One atomic per warp.
-__device__ __forceinline__ bool buffer_append(unsigned long long* buf, Shared& sm, int cap, bool want,
-                                              unsigned long long key) {
+// Appends `key` from every lane whose `want` is set; false for a lane whose entry did not fit.
+// The whole warp calls it together.  One shared-memory atomic per warp.
+__device__ __forceinline__ bool warp_append(unsigned long long* dst, int* counter, int limit, bool want,
+                                            unsigned long long key) {
   unsigned mask = __ballot_sync(FULL, want);
   if (mask == 0) return true;
   int lane = threadIdx.x & 31;
   int leader = __ffs(mask) - 1;
   int base = 0;
-  if (lane == leader) base = atomicAdd(&sm.n, __popc(mask));
+  if (lane == leader) base = atomicAdd(counter, __popc(mask));
   base = __shfl_sync(FULL, base, leader);
   if (!want) return true;
   int slot = base + __popc(mask & ((1u << lane) - 1u));
-  if (slot < cap) { buf[slot] = key; return true; }
+  if (slot < limit) { dst[slot] = key; return true; }
   return false;
 }
 
 // Rebuilds the buffer around a new threshold.  All threads of the block call it together, after a
-// barrier that made every append visible.  mode M_SELECT_K: the threshold is the k-th largest
-// value held (none if fewer than k are held); mode M_SELECT_MINP: the largest value held plus
-// log(min_p).  Every entry at or above the threshold stays; sm.tau becomes the threshold.
-__device__ inline void buffer_rebuild(unsigned long long* buf, unsigned* hist, Shared& sm, int cap,
-                                      int keep, int mode, int k, float logm) {
-  const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
-  const int n = min(sm.n, cap);
-  unsigned long long e[EPT];
-#pragma unroll
-  for (int j = 0; j < EPT; ++j) {
-    int i = j * nt + tid;
-    e[j] = (i < n) ? buf[i] : 0ull;
-  }
-  if (tid == 0) { sm.diff = 0u; sm.vmax = 0u; }
-  __syncthreads();  // every entry is in registers; sm.n may be reset below
-  uint32_t thr = 0u;
-  if (mode == M_SELECT_MINP) {
-    uint32_t mx = 0u;
-#pragma unroll
-    for (int j = 0; j < EPT; ++j) mx = max(mx, key_vbits(e[j]));
+// barrier that made every append visible.  M_SELECT_K: the threshold is a score with at least k
+// and at most `keep` entries at or above it, found coarse to fine: 2048 buckets over the range the
+// entries span, then over the bucket that holds the k-th largest, until few enough remain (the
+// k-th largest itself at the finest step).  M_SELECT_MINP: the largest score held plus log(min_p).
+// Every entry at or above the threshold stays; sm.tau becomes the threshold.
+__device__ __noinline__ void buffer_rebuild(Ctx c) {
+  Shared& sm = *c.sm;
+  unsigned long long* buf = c.buf;
+  unsigned* hist = c.hist;
+  unsigned* wtot = c.hist + BINS;
+  const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
+  const int n = min(sm.n, c.cap);
+  if (tid == 0) { sm.vmin = 0xFFFFFFFFu; sm.vmax = 0u; sm.m = 0; }
+  __syncthreads();
+  {
+    uint32_t mx = 0u, mn = 0xFFFFFFFFu;
+    for (int i = tid; i < n; i += nt) {
+      uint32_t v = key_vbits(buf[i]);
+      mx = max(mx, v);
+      mn = min(mn, v);
+    }
     mx = __reduce_max_sync(FULL, mx);
-    if (lane == 0) atomicMax(&sm.vmax, mx);
-    __syncthreads();
-    thr = ord32(unord32(sm.vmax) + logm + 0.0f);
-  } else if (n > k) {
-    const uint32_t ref = key_vbits(buf[0]);
-    uint32_t d = 0u;
-#pragma unroll
-    for (int j = 0; j < EPT; ++j)
-      if (e[j]) d |= key_vbits(e[j]) ^ ref;
-    d = __reduce_or_sync(FULL, d);
-    if (lane == 0 && d) atomicOr(&sm.diff, d);
-    __syncthreads();
-    const uint32_t diff = sm.diff;
-    if (diff == 0u) {
-      thr = ref;
-    } else {
-      int shift = ((31 - __clz(diff)) >> 3) << 3;
-      uint32_t known = (shift + 8 >= 32) ? 0u : (0xFFFFFFFFu << (shift + 8));
-      uint32_t prefix = ref & known;
-      int rem = k;
-      for (; shift >= 0; shift -= 8) {
-        for (int i = tid; i < 256; i += nt) hist[i] = 0u;
-        __syncthreads();
-#pragma unroll
-        for (int j = 0; j < EPT; ++j) {
-          uint32_t v = key_vbits(e[j]);
-          if (e[j] && (v & known) == prefix) atomicAdd(&hist[(v >> shift) & 255u], 1u);
-        }
-        __syncthreads();
-        if (tid < 32) {
-          // lane L owns bins 255-8L .. 248-8L, highest first
-          unsigned c[8];
-          unsigned local = 0;
-#pragma unroll
-          for (int q = 0; q < 8; ++q) { c[q] = hist[255 - 8 * lane - q]; local += c[q]; }
-          unsigned incl = local;
-#pragma unroll
-          for (int dd = 1; dd < 32; dd <<= 1) {
-            unsigned o = __shfl_up_sync(FULL, incl, dd);
-            if (lane >= dd) incl += o;
-          }
-          unsigned excl = incl - local;
-          if (excl < (unsigned)rem && (unsigned)rem <= incl) {
-            unsigned acc = excl;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              if (acc < (unsigned)rem && (unsigned)rem <= acc + c[q]) {
-                sm.sel_bin = 255 - 8 * lane - q;
-                sm.sel_rem = rem - (int)acc;
-              }
-              acc += c[q];
-            }
-          }
-        }
-        __syncthreads();
-        prefix |= ((uint32_t)sm.sel_bin) << shift;
-        known |= 255u << shift;
-        rem = sm.sel_rem;
+    mn = __reduce_min_sync(FULL, mn);
+    if (lane == 0) { atomicMax(&sm.vmax, mx); atomicMin(&sm.vmin, mn); }
+  }
+  __syncthreads();
+  uint32_t thr = 0u;
+  if (c.mode == M_SELECT_MINP) {
+    thr = ord32(unord32(sm.vmax) + c.logm + 0.0f);
+  } else if (n > c.k) {
+    uint32_t lo = sm.vmin, hi = sm.vmax;  // the k-th largest lies in [lo, hi]
+    unsigned above = 0u;                  // entries above hi
+    unsigned rem = (unsigned)c.k;         // the one sought is the rem-th largest within [lo, hi]
+    const int per = BINS / nt;
+    for (int pass = 0; pass < 4; ++pass) {
+      const uint32_t range = hi - lo;
+      if (range == 0u) { thr = lo; break; }
+      const int bits = 32 - __clz(range);
+      const int shift = bits > 11 ? bits - 11 : 0;
+      for (int i = tid; i < BINS; i += nt) hist[i] = 0u;
+      __syncthreads();
+      for (int i = tid; i < n; i += nt) {
+        uint32_t v = key_vbits(buf[i]);
+        if (v >= lo && v <= hi) atomicAdd(&hist[(v - lo) >> shift], 1u);
       }
-      thr = prefix;
-    }
-  }
-  if (tid == 0) sm.n = 0;
-  __syncthreads();
+      __syncthreads();
+      // thread t owns buckets BINS-1 - t*per - j, j < per: highest first
+      unsigned local = 0u;
+      for (int j = 0; j < per; ++j) local += hist[BINS - 1 - tid * per - j];
+      unsigned incl = local;
 #pragma unroll
-  for (int j = 0; j < EPT; ++j) {
-    if (j * nt < n) {  // uniform across the block
-      bool want = e[j] != 0ull && key_vbits(e[j]) >= thr;
-      buffer_append(buf, sm, cap, want, e[j]);
+      for (int d = 1; d < 32; d <<= 1) {
+        unsigned o = __shfl_up_sync(FULL, incl, d);
+        if (lane >= d) incl += o;
+      }
+      if (lane == 31) wtot[warp] = incl;
+      __syncthreads();
+      unsigned before = 0u;
+      for (int w = 0; w < warp; ++w) before += wtot[w];
+      unsigned acc = before + incl - local;  // entries in buckets above this thread's
+      if (acc < rem && rem <= acc + local) {
+        for (int j = 0; j < per; ++j) {
+          unsigned cnt = hist[BINS - 1 - tid * per - j];
+          if (acc < rem && rem <= acc + cnt) {
+            sm.sel_bin = BINS - 1 - tid * per - j;
+            sm.sel_above = (int)acc;
+            sm.sel_count = (int)cnt;
+          }
+          acc += cnt;
+        }
+      }
+      __syncthreads();
+      const uint32_t edge = lo + ((uint32_t)sm.sel_bin << shift);
+      const unsigned at_or_above = above + (unsigned)sm.sel_above + (unsigned)sm.sel_count;
+      if (at_or_above <= (unsigned)c.keep || shift == 0) { thr = edge; break; }
+      above += (unsigned)sm.sel_above;
+      rem -= (unsigned)sm.sel_above;
+      const uint32_t last = edge + ((1u << shift) - 1u);
+      lo = edge;
+      hi = last < hi ? last : hi;
+      (void)nwarps;
     }
   }
-  __syncthreads();
-  if (tid == 0) {
-    if (thr != 0u) sm.tau = fmaxf(sm.tau, unord32(thr));
-    if (sm.n > keep) sm.overflow = 1;
+  if (thr != 0u) {
+    // survivors go to the staging area, then back to the front of the buffer
+    for (int base = 0; base < n; base += nt) {
+      int i = base + tid;
+      unsigned long long key = (i < n) ? buf[i] : 0ull;
+      warp_append(c.stage, &sm.m, c.keep, i < n && key_vbits(key) >= thr, key);
+    }
+    __syncthreads();
+    const int m = min(sm.m, c.keep);
+    for (int i = tid; i < m; i += nt) buf[i] = c.stage[i];
+    if (tid == 0) {
+      if (sm.m > c.keep) sm.overflow = 1;
+      sm.n = m;
+      sm.tau = fmaxf(sm.tau, unord32(thr));
+    }
+  } else if (tid == 0) {
+    sm.n = n;
+    if (n >= c.cap) sm.overflow = 1;  // cannot happen while cap > k
   }
   __syncthreads();
 }
 
-// Appends one optional entry per thread, rebuilding the buffer as often as it takes.  Block-wide.
-__device__ inline void buffer_push(unsigned long long* buf, unsigned* hist, Shared& sm, int cap, int keep,
-                                   int mode, int k, float logm, bool want, unsigned long long key) {
+// Block-synchronous append of one optional entry per thread (the merge of a row's slices).
+__device__ inline void buffer_push(Ctx c, bool want, unsigned long long key) {
+  Shared& sm = *c.sm;
   bool pending = want && key_value(key) >= sm.tau;
   while (true) {
-    bool ok = buffer_append(buf, sm, cap, pending, key);
+    bool ok = warp_append(c.buf, &sm.n, c.cap, pending, key);
     pending = pending && !ok;
     if (!__syncthreads_or(pending ? 1 : 0)) break;
-    buffer_rebuild(buf, hist, sm, cap, keep, mode, k, logm);
+    buffer_rebuild(c);
     if (sm.overflow) break;
     pending = pending && key_value(key) >= sm.tau;
   }
@@ -277,16 +306,42 @@ __device__ inline void block_sort_desc(unsigned long long* buf, int p2) {
 
 // ---- finishing a row ----------------------------------------------------------------------------
 
+// A row that did not go through the candidate buffer: greedy, whole-row Gumbel argmax, or one the
+// single pass could not reduce.
+__device__ inline void finish_simple(const KParams& P, int b, int mode, unsigned long long best,
+                                     unsigned long long gbest, bool failed) {
+  for (int j = threadIdx.x; j < P.out_width; j += blockDim.x) {
+    if (P.out_probs) P.out_probs[(size_t)b * P.out_width + j] = 0.0f;
+    if (P.out_prob_ids) P.out_prob_ids[(size_t)b * P.out_width + j] = -1;
+  }
+  if (threadIdx.x != 0) return;
+  int id = (mode == M_ARGMAX_L) ? key_id(gbest) : key_id(best);
+  if (failed) {
+    id = -1;
+    if (P.ws_flag && !(P.flags & 2u)) P.ws_flag[b] = 1;
+    else if (P.status) atomicOr(P.status, 4);
+  }
+  if (P.out_ids) P.out_ids[b] = id;
+  if (failed) return;
+  if (P.out_cut) P.out_cut[b] = (mode == M_ARGMAX_G) ? neg_inf() : quiet_nan();
+  if (P.out_kept) P.out_kept[b] = (mode == M_ARGMAX_G) ? P.vocab : 0;
+  if (mode == M_ARGMAX_G && P.out_probs && P.status) atomicOr(P.status, 2);
+}
+
 // buf[0..sm.n) holds the row's candidates (unsorted).  Computes the cut and the draw and writes the
 // row's outputs.  fw / fi / fs are float scratch of cap, cap and cap/32 entries.
 __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, unsigned long long* buf,
                                   Shared& sm, float* fw, float* fi, float* fs, float row_min) {
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
   const int n = sm.n;
+  if (n <= 0) {  // nothing comparable in the row (all NaN)
+    finish_simple(P, b, rc.mode, 0ull, 0ull, true);
+    return;
+  }
   int p2 = 1;
   while (p2 < n) p2 <<= 1;
   for (int i = n + tid; i < p2; i += nt) buf[i] = 0ull;
-  if (tid == 0) { sm.jstar = 0; sm.ns = 0; sm.pick = 0x7FFFFFFF; sm.best = 0ull; }
+  if (tid == 0) { sm.jstar = 0; sm.ns = 0; sm.pick = NO_ID; sm.best = 0ull; }
   __syncthreads();
   block_sort_desc(buf, p2);
   const float top = key_value(buf[0]);
@@ -364,32 +419,48 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
   }
 }
 
-// A row that did not go through the candidate buffer: greedy, whole-row Gumbel argmax, or one the
-// single pass could not reduce.
-__device__ inline void finish_simple(const KParams& P, const RowCfg& rc, int b, int mode,
-                                     unsigned long long best, unsigned long long gbest, bool failed) {
-  if (threadIdx.x != 0) return;
-  int id = (mode == M_ARGMAX_L) ? key_id(gbest) : key_id(best);
-  if (failed) {
-    id = -1;
-    if (P.ws_flag && !(P.flags & 2u)) P.ws_flag[b] = 1;
-    else if (P.status) atomicOr(P.status, 4);
+// ---- streaming a slice --------------------------------------------------------------------------
+
+struct History {
+  const unsigned* bitmap;
+  const int* keys;
+  const int* counts;
+  int mask;
+  int begin;
+};
+
+__device__ __forceinline__ int history_count(const History& h, int idx) {
+  int local = idx - h.begin;
+  if (!((h.bitmap[local >> 5] >> (local & 31)) & 1u)) return 0;
+  uint32_t slot = lowbias32((uint32_t)idx) & h.mask;
+  for (int probe = 0; probe <= h.mask; ++probe) {
+    int k = h.keys[slot];
+    if (k == idx) return h.counts[slot];
+    if (k == HASH_EMPTY) return 0;
+    slot = (slot + 1) & h.mask;
   }
-  if (P.out_ids) P.out_ids[b] = id;
-  if (failed) return;
-  if (P.out_cut) P.out_cut[b] = (mode == M_ARGMAX_G) ? neg_inf() : quiet_nan();
-  if (P.out_kept) P.out_kept[b] = (mode == M_ARGMAX_G) ? P.vocab : 0;
-  if (mode == M_ARGMAX_G && P.out_probs && P.status) atomicOr(P.status, 2);
+  return 0;
 }
 
-__device__ inline void clear_probs(const KParams& P, int b) {
-  for (int j = threadIdx.x; j < P.out_width; j += blockDim.x) {
-    if (P.out_probs) P.out_probs[(size_t)b * P.out_width + j] = 0.0f;
-    if (P.out_prob_ids) P.out_prob_ids[(size_t)b * P.out_width + j] = -1;
+// the penalised logit of element idx, whose raw logit is l
+template <bool PEN>
+__device__ __forceinline__ float exact_logit(const KParams& P, const RowCfg& rc, const History& h,
+                                             const uint8_t* seen_row, int idx, float l) {
+  if (PEN) {
+    int count = P.history ? history_count(h, idx) : 0;
+    if (seen_row && seen_row[idx]) count = max(count, 1);
+    if (count) l = penalised(l, count, rc);
   }
+  return l;
 }
 
-// ---- the kernel ---------------------------------------------------------------------------------
+template <int N>
+__device__ __forceinline__ float pick(const float (&v)[N], int q) {
+  float r = v[0];
+#pragma unroll
+  for (int i = 1; i < N; ++i) r = (q == i) ? v[i] : r;
+  return r;
+}
 
 template <int VEC>
 struct Chunk {
@@ -417,29 +488,175 @@ __device__ __forceinline__ void load_chunk(Chunk<VEC>& c, const float* __restric
   }
 }
 
-__device__ __forceinline__ int hash_count(const int* hk, const int* hc, int ht_mask, int id) {
-  uint32_t slot = lowbias32((uint32_t)id) & ht_mask;
-  for (int probe = 0; probe <= ht_mask; ++probe) {
-    int k = hk[slot];
-    if (k == id) return hc[slot];
-    if (k == HASH_EMPTY) return 0;
-    slot = (slot + 1) & ht_mask;
+struct Tracked {
+  float gl; int gid;  // best penalised logit and where (greedy)
+  float al; int aid;  // best score + gumbel and where
+  float mnl;          // smallest raw unpenalised logit
+  float mns;          // smallest score among penalised elements
+};
+
+// Streams [begin, end) of one row.  MODE is the row's mode; every warp of the block runs this with
+// the same arguments.
+template <int VEC, bool PEN, int MODE>
+__device__ __forceinline__ void stream_slice(const KParams& P, const RowCfg& rc, Ctx c, const History& h,
+                                             const float* __restrict__ row,
+                                             const uint8_t* __restrict__ seen_row, int begin, int end,
+                                             Tracked& t) {
+  Shared& sm = *c.sm;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int off = P.vocab_offset;
+  constexpr bool SELECT = (MODE == M_SELECT_K || MODE == M_SELECT_MINP);
+  int from = begin;
+  if (SELECT) {
+    // the first `cap` elements go straight into the buffer
+    const int fill_end = min(end, begin + c.cap);
+    for (int i = begin + tid; i < fill_end; i += nt) {
+      float l = exact_logit<PEN>(P, rc, h, seen_row, i, row[i]);
+      if (rc.track && (l > t.gl || (l == t.gl && i < t.gid))) { t.gl = l; t.gid = i; }
+      float s = scaled(l, rc);
+      if (!(s == s)) s = neg_inf();
+      if (MODE == M_SELECT_MINP) t.mns = fminf(t.mns, s);
+      c.buf[i - begin] = make_key(s, (uint32_t)(i + off));
+    }
+    __syncthreads();
+    if (tid == 0) sm.n = fill_end - begin;
+    __syncthreads();
+    if (end > fill_end) buffer_rebuild(c);
+    from = fill_end;
   }
-  return 0;
+  float tau = sm.tau;
+  float floor_l = logit_floor(tau, rc.tf);
+  bool stop = SELECT && sm.overflow;
+  const int stride = nt * VEC;
+  const int span = stride * UNROLL;
+  Chunk<VEC> cur, nxt;
+  if (!stop) load_chunk<VEC, PEN>(cur, row, seen_row, from + tid * VEC, stride, end);
+  for (int base = from; base < end && !stop; base += span) {
+    const int first = base + tid * VEC;
+    if (base + span < end) load_chunk<VEC, PEN>(nxt, row, seen_row, first + span, stride, end);
+    unsigned pm = 0u;  // elements that need the exact path
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int idx = first + u * stride;
+      unsigned flagged = 0u;
+      if (PEN) {
+        if (idx < end) {
+          int local = idx - begin;
+          if (P.history) flagged = (h.bitmap[local >> 5] >> (local & 31)) & ((1u << VEC) - 1u);
+          flagged |= cur.seen[u];
+        }
+      }
+      if (PEN && flagged) {
+        pm |= ((1u << VEC) - 1u) << (u * VEC);
+      } else {
+        float m4 = cur.v[u * VEC];
+#pragma unroll
+        for (int e = 1; e < VEC; ++e) m4 = fmaxf(m4, cur.v[u * VEC + e]);
+        if (MODE == M_SELECT_MINP) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) t.mnl = fminf(t.mnl, cur.v[u * VEC + e]);
+        }
+        if (MODE == M_ARGMAX_G) {
+          // score + gumbel can only win if score + the largest gumbel reaches the best so far
+          if (scaled(m4, rc) + GUMBEL_MAX >= t.al) pm |= ((1u << VEC) - 1u) << (u * VEC);
+          if (rc.track && m4 > t.gl) pm |= ((1u << VEC) - 1u) << (u * VEC);
+        } else {
+          if (rc.track && m4 > t.gl) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+              float l = cur.v[u * VEC + e];
+              if (l > t.gl) { t.gl = l; t.gid = idx + e; }
+            }
+          }
+          if (SELECT && m4 >= floor_l) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+              if (cur.v[u * VEC + e] >= floor_l) pm |= 1u << (u * VEC + e);
+          }
+        }
+      }
+    }
+    // the exact path, one element per lane per round; an element whose entry does not fit is
+    // redone after the block has rebuilt the buffer
+    unsigned redo = 0u;
+    int rounds = 0;
+    while (true) {
+      while (__any_sync(FULL, pm != 0u)) {
+        const bool have = pm != 0u;
+        const int q = have ? __ffs(pm) - 1 : 0;
+        pm &= pm - 1u;
+        const int idx = first + (q / VEC) * stride + (q % VEC);
+        bool want = false;
+        unsigned long long key = 0ull;
+        if (have && idx < end) {
+          float l = exact_logit<PEN>(P, rc, h, seen_row, idx, pick(cur.v, q));
+          if (rc.track && (l > t.gl || (l == t.gl && idx < t.gid))) { t.gl = l; t.gid = idx; }
+          float s = scaled(l, rc);
+          if (MODE == M_SELECT_MINP) t.mns = fminf(t.mns, s);
+          if (MODE == M_ARGMAX_G) {
+            if (s + GUMBEL_MAX >= t.al) {
+              float d = s + gumbel(hashed_uniform((uint32_t)(idx + off), rc.rkey));
+              if (d > t.al || (d == t.al && idx < t.aid)) { t.al = d; t.aid = idx; }
+            }
+          } else if (SELECT) {
+            want = s >= tau;
+            key = make_key(s, (uint32_t)(idx + off));
+          }
+        }
+        if (SELECT) {
+          const bool fit = warp_append(c.buf, &sm.n, c.cap, want, key);  // every lane calls it
+          if (want && !fit) redo |= 1u << q;
+        }
+      }
+      if (!SELECT) break;
+      // one barrier per step: did any warp run out of buffer?
+      if (!__syncthreads_or(redo != 0u)) break;
+      buffer_rebuild(c);
+      tau = sm.tau;
+      floor_l = logit_floor(tau, rc.tf);
+      if (sm.overflow || ++rounds > 64) {
+        if (tid == 0) sm.overflow = 1;
+        stop = true;
+        break;
+      }
+      pm = redo;
+      redo = 0u;
+    }
+    cur = nxt;
+  }
 }
 
+// ---- the kernel ---------------------------------------------------------------------------------
+
+struct SmemMap {
+  unsigned long long* buf;
+  unsigned long long* stage;
+  unsigned* hist;
+  Shared* sm;
+  unsigned char* region;  // streaming: bitmap + hash table; finishing: float scratch
+};
+
+__device__ __forceinline__ SmemMap smem_map(unsigned char* raw, int cap, int keep) {
+  SmemMap m;
+  m.buf = reinterpret_cast<unsigned long long*>(raw);
+  m.stage = m.buf + cap;
+  m.hist = reinterpret_cast<unsigned*>(m.stage + keep);
+  m.sm = reinterpret_cast<Shared*>(m.hist + BINS + 32);
+  m.region = reinterpret_cast<unsigned char*>(m.hist + BINS + 32) + 128;
+  return m;
+}
+static_assert(sizeof(Shared) <= 128, "Shared must fit its slot");
+
 template <int VEC, bool PEN>
-__global__ void __launch_bounds__(512) sample_kernel(const KParams P) {
+__global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  unsigned long long* buf = reinterpret_cast<unsigned long long*>(smem_raw);
-  unsigned* hist = reinterpret_cast<unsigned*>(smem_raw + (size_t)P.cap * 8);
-  Shared& sm = *reinterpret_cast<Shared*>(hist + 256);
-  unsigned char* region = reinterpret_cast<unsigned char*>(hist + 256) + 128;
-  static_assert(sizeof(Shared) <= 128, "Shared must fit its slot");
-  unsigned* bitmap = reinterpret_cast<unsigned*>(region);
+  const SmemMap M = smem_map(smem_raw, P.cap, P.keep);
+  unsigned long long* buf = M.buf;
+  Shared& sm = *M.sm;
+  unsigned* bitmap = reinterpret_cast<unsigned*>(M.region);
   int* hkeys = reinterpret_cast<int*>(bitmap + P.bm_words);
   int* hcnt = hkeys + P.ht_size;
-  float* fw = reinterpret_cast<float*>(region);
+  float* fw = reinterpret_cast<float*>(M.region);
   float* fi = fw + P.cap;
   float* fs = fi + P.cap;
 
@@ -447,36 +664,38 @@ __global__ void __launch_bounds__(512) sample_kernel(const KParams P) {
   const int b = blockIdx.y, slice = blockIdx.x, S = P.slices;
   const RowCfg rc = row_config(P, b);
   const int mode = rc.mode;
-  const bool divide = (P.flags & 1u) != 0u;
-  const float tfloor = fmaxf(rc.T, 1e-6f);
   const int begin = slice * P.slice_len;
   const int end = min(P.vocab, begin + P.slice_len);
   const float* row = P.logits + (size_t)b * P.row_stride;
   const uint8_t* seen_row = (PEN && P.seen) ? P.seen + (size_t)b * P.seen_stride : nullptr;
+  Ctx c;
+  c.buf = buf; c.stage = M.stage; c.hist = M.hist; c.sm = M.sm;
+  c.cap = P.cap; c.keep = P.keep; c.mode = mode; c.k = rc.k_eff; c.logm = rc.logm;
 
   if (tid == 0) {
-    sm.n = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.best = 0ull; sm.gbest = 0ull;
+    sm.n = 0; sm.m = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.best = 0ull; sm.gbest = 0ull;
     sm.smin = 0xFFFFFFFFu; sm.is_last = (S == 1);
   }
-  const int ht_mask = P.ht_size - 1;
-  if (PEN) {
+  History h;
+  h.bitmap = bitmap; h.keys = hkeys; h.counts = hcnt; h.mask = P.ht_size - 1; h.begin = begin;
+  if (PEN && P.history) {
     for (int i = tid; i < P.bm_words; i += nt) bitmap[i] = 0u;
     for (int i = tid; i < P.ht_size; i += nt) { hkeys[i] = HASH_EMPTY; hcnt[i] = 0; }
   }
   __syncthreads();
   if (PEN && P.history) {
     const int hl = P.history_len ? min(P.history_len[b], P.history_cap) : P.history_cap;
-    const int* h = P.history + (size_t)b * P.history_cap;
+    const int* hist_ids = P.history + (size_t)b * P.history_cap;
     for (int i = tid; i < hl; i += nt) {
-      int id = h[i] - P.vocab_offset;
+      int id = hist_ids[i] - P.vocab_offset;
       if (id >= begin && id < end) {
         int local = id - begin;
         atomicOr(&bitmap[local >> 5], 1u << (local & 31));
-        uint32_t slot = lowbias32((uint32_t)id) & ht_mask;
-        for (int probe = 0; probe <= ht_mask; ++probe) {
+        uint32_t slot = lowbias32((uint32_t)id) & h.mask;
+        for (int probe = 0; probe <= h.mask; ++probe) {
           int old = atomicCAS(&hkeys[slot], HASH_EMPTY, id);
           if (old == HASH_EMPTY || old == id) { atomicAdd(&hcnt[slot], 1); break; }
-          slot = (slot + 1) & ht_mask;
+          slot = (slot + 1) & h.mask;
         }
       }
     }
@@ -484,108 +703,43 @@ __global__ void __launch_bounds__(512) sample_kernel(const KParams P) {
   }
 
   // ---- stream the slice once ----
-  float gl = neg_inf();     // this thread's best penalised logit and where
-  int gid = 0x7FFFFFFF;
-  float al = neg_inf();     // this thread's best score + gumbel and where
-  int aid = 0x7FFFFFFF;
-  float mn = __uint_as_float(0x7F800000u);  // this thread's smallest score
-  if (mode != M_GENERAL) {
-    const int stride = nt * VEC;
-    const int span = stride * UNROLL;
-    Chunk<VEC> cur, nxt;
-    load_chunk<VEC, PEN>(cur, row, seen_row, begin + tid * VEC, stride, end);
-    for (int base = begin; base < end; base += span) {
-      const int first = base + tid * VEC;
-      if (base + span < end) load_chunk<VEC, PEN>(nxt, row, seen_row, first + span, stride, end);
-      float tau = sm.tau;
-      unsigned pend = 0u;
-      float sv[UNROLL * VEC];
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const int idx = first + u * stride;
-        unsigned hbits = 0u;
-        if (PEN) {
-          int local = idx - begin;
-          if (idx < end) {
-            if (P.history) hbits = (bitmap[local >> 5] >> (local & 31)) & ((1u << VEC) - 1u);
-          }
-        }
-#pragma unroll
-        for (int c = 0; c < VEC; ++c) {
-          float l = cur.v[u * VEC + c];
-          if (PEN) {
-            unsigned sbyte = (cur.seen[u] >> (8 * c)) & 255u;
-            if (((hbits >> c) & 1u) | sbyte) {
-              int cnt = ((hbits >> c) & 1u) ? hash_count(hkeys, hcnt, ht_mask, idx + c) : 0;
-              cnt = max(cnt, sbyte ? 1 : 0);
-              l = penalised(l, cnt, rc);
-            }
-          }
-          if (rc.track && l > gl) { gl = l; gid = idx + c; }
-          float s = scaled(l, rc, divide, tfloor);
-          sv[u * VEC + c] = s;
-          if (mode == M_ARGMAX_G) {
-            if (idx + c < end) {
-              float d = s + gumbel(hashed_uniform((uint32_t)(idx + c + P.vocab_offset), rc.rkey));
-              if (d > al) { al = d; aid = idx + c; }
-            }
-          } else if (mode >= M_SELECT_K) {
-            if (s >= tau) pend |= 1u << (u * VEC + c);
-            if (mode == M_SELECT_MINP) mn = fminf(mn, s);
-          }
-        }
-      }
-      if (mode >= M_SELECT_K) {
-        while (true) {
-          if (__any_sync(FULL, pend != 0u)) {
-#pragma unroll
-            for (int q = 0; q < UNROLL * VEC; ++q) {
-              bool want = (pend >> q) & 1u;
-              int id = first + (q / VEC) * stride + (q % VEC) + P.vocab_offset;
-              if (buffer_append(buf, sm, P.cap, want, make_key(sv[q], (uint32_t)id))) pend &= ~(1u << q);
-            }
-          }
-          if (!__syncthreads_or(pend != 0u)) break;
-          buffer_rebuild(buf, hist, sm, P.cap, P.keep, mode, rc.k_eff, rc.logm);
-          if (sm.overflow) { pend = 0u; break; }
-          tau = sm.tau;
-#pragma unroll
-          for (int q = 0; q < UNROLL * VEC; ++q)
-            if (!(sv[q] >= tau)) pend &= ~(1u << q);
-        }
-        if (sm.overflow) break;
-      }
-      cur = nxt;
-    }
-  }
+  Tracked t;
+  t.gl = neg_inf(); t.gid = NO_ID; t.al = neg_inf(); t.aid = NO_ID;
+  t.mnl = __uint_as_float(0x7F800000u); t.mns = t.mnl;
+  if (mode == M_ARGMAX_L) stream_slice<VEC, PEN, M_ARGMAX_L>(P, rc, c, h, row, seen_row, begin, end, t);
+  else if (mode == M_ARGMAX_G) stream_slice<VEC, PEN, M_ARGMAX_G>(P, rc, c, h, row, seen_row, begin, end, t);
+  else if (mode == M_SELECT_K) stream_slice<VEC, PEN, M_SELECT_K>(P, rc, c, h, row, seen_row, begin, end, t);
+  else if (mode == M_SELECT_MINP) stream_slice<VEC, PEN, M_SELECT_MINP>(P, rc, c, h, row, seen_row, begin, end, t);
   __syncthreads();
 
   // ---- reduce what the slice found ----
   if (rc.track) {
-    unsigned long long g = (gid != 0x7FFFFFFF) ? make_key(gl, (uint32_t)(gid + P.vocab_offset)) : 0ull;
+    unsigned long long g = (t.gid != NO_ID) ? make_key(t.gl, (uint32_t)(t.gid + P.vocab_offset)) : 0ull;
+    if (tid == 0 && begin < end) g = max(g, make_key(neg_inf(), (uint32_t)(begin + P.vocab_offset)));
     g = warp_max_u64(g);
     if (lane == 0) atomicMax(&sm.gbest, g);
   }
   if (mode == M_ARGMAX_G) {
-    unsigned long long a = (aid != 0x7FFFFFFF) ? make_key(al, (uint32_t)(aid + P.vocab_offset)) : 0ull;
+    unsigned long long a = (t.aid != NO_ID) ? make_key(t.al, (uint32_t)(t.aid + P.vocab_offset)) : 0ull;
+    if (tid == 0 && begin < end) a = max(a, make_key(neg_inf(), (uint32_t)(begin + P.vocab_offset)));
     a = warp_max_u64(a);
     if (lane == 0) atomicMax(&sm.best, a);
   }
   if (mode == M_SELECT_MINP) {
-    unsigned m = __reduce_min_sync(FULL, ord32(mn));
+    float mn = fminf(t.mns, scaled(t.mnl, rc));
+    unsigned m = __reduce_min_sync(FULL, ord32(mn + 0.0f));
     if (lane == 0) atomicMin(&sm.smin, m);
   }
   __syncthreads();
-  if (mode >= M_SELECT_K && mode != M_GENERAL && !sm.overflow) {
-    if (mode == M_SELECT_MINP || sm.n > rc.k_eff)
-      buffer_rebuild(buf, hist, sm, P.cap, P.keep, mode, rc.k_eff, rc.logm);
+  if ((mode == M_SELECT_K || mode == M_SELECT_MINP) && !sm.overflow) {
+    if (mode == M_SELECT_MINP || sm.n > rc.k_eff) buffer_rebuild(c);
   }
   bool failed = (mode == M_GENERAL) || sm.overflow;
 
   // ---- publish, and let the last block of the row go on ----
   if (S > 1) {
     const size_t cell = (size_t)b * S + slice;
-    if (mode >= M_SELECT_K && !failed) {
+    if ((mode == M_SELECT_K || mode == M_SELECT_MINP) && !failed) {
       const int n = sm.n;
       unsigned long long* dst = P.ws_keys + cell * P.keep;
       for (int i = tid; i < n; i += nt) dst[i] = buf[i];
@@ -599,8 +753,8 @@ __global__ void __launch_bounds__(512) sample_kernel(const KParams P) {
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-      unsigned t = atomicAdd(&P.ws_ticket[b], 1u);
-      sm.is_last = (t == (unsigned)(S - 1));
+      unsigned ticket = atomicAdd(&P.ws_ticket[b], 1u);
+      sm.is_last = (ticket == (unsigned)(S - 1));
       if (sm.is_last) P.ws_ticket[b] = 0u;
     }
     __syncthreads();
@@ -625,7 +779,7 @@ __global__ void __launch_bounds__(512) sample_kernel(const KParams P) {
     mnb = __reduce_min_sync(FULL, mnb);
     if (lane == 0) { atomicMax(&sm.gbest, g); atomicMax(&sm.best, a); atomicMin(&sm.smin, mnb); }
     failed = __syncthreads_or(bad) != 0;
-    if (mode >= M_SELECT_K && !failed) {
+    if ((mode == M_SELECT_K || mode == M_SELECT_MINP) && !failed) {
       const int total_slots = S * P.keep;
       for (int base = 0; base < total_slots; base += nt) {
         int i = base + tid;
@@ -636,12 +790,11 @@ __global__ void __launch_bounds__(512) sample_kernel(const KParams P) {
           key = __ldcg(&P.ws_keys[((size_t)b * S + j) * P.keep + q]);
           want = true;
         }
-        buffer_push(buf, hist, sm, P.cap, P.keep, mode, rc.k_eff, rc.logm, want, key);
+        buffer_push(c, want, key);
         if (sm.overflow) break;
       }
       __syncthreads();
-      if (!sm.overflow && (mode == M_SELECT_MINP || sm.n > rc.k_eff))
-        buffer_rebuild(buf, hist, sm, P.cap, P.keep, mode, rc.k_eff, rc.logm);
+      if (!sm.overflow && (mode == M_SELECT_MINP || sm.n > rc.k_eff)) buffer_rebuild(c);
       failed = sm.overflow != 0;
     }
   }
@@ -651,7 +804,7 @@ __global__ void __launch_bounds__(512) sample_kernel(const KParams P) {
   if (P.cand_count) {  // shard mode: hand the row's candidates to the gather
     const int cap = P.cand_cap;
     int n = 0;
-    if (!failed && mode >= M_SELECT_K) {
+    if (!failed && (mode == M_SELECT_K || mode == M_SELECT_MINP)) {
       n = sm.n;
       if (n > cap) { n = 0; failed = true; }
       for (int i = tid; i < n; i += nt) {
@@ -673,8 +826,7 @@ __global__ void __launch_bounds__(512) sample_kernel(const KParams P) {
   }
   if (tid == 0 && P.out_greedy) P.out_greedy[b] = key_id(sm.gbest);
   if (failed || mode < M_SELECT_K) {
-    finish_simple(P, rc, b, mode, sm.best, sm.gbest, failed);
-    clear_probs(P, b);
+    finish_simple(P, b, mode, sm.best, sm.gbest, failed);
     return;
   }
   finish_row(P, rc, b, buf, sm, fw, fi, fs, unord32(sm.smin));
@@ -683,19 +835,22 @@ __global__ void __launch_bounds__(512) sample_kernel(const KParams P) {
 // Finishes rows from candidates gathered from `g_parts` vocabulary slices: one block per row.
 __global__ void __launch_bounds__(512) finish_candidates_kernel(const KParams P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  unsigned long long* buf = reinterpret_cast<unsigned long long*>(smem_raw);
-  unsigned* hist = reinterpret_cast<unsigned*>(smem_raw + (size_t)P.cap * 8);
-  Shared& sm = *reinterpret_cast<Shared*>(hist + 256);
-  unsigned char* region = reinterpret_cast<unsigned char*>(hist + 256) + 128;
-  float* fw = reinterpret_cast<float*>(region);
+  const SmemMap M = smem_map(smem_raw, P.cap, P.keep);
+  unsigned long long* buf = M.buf;
+  Shared& sm = *M.sm;
+  float* fw = reinterpret_cast<float*>(M.region);
   float* fi = fw + P.cap;
   float* fs = fi + P.cap;
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
   const int b = blockIdx.x, parts = P.g_parts, cap = P.cand_cap, rows = P.rows;
   const RowCfg rc = row_config(P, b);
   const int mode = rc.mode;
+  Ctx c;
+  c.buf = buf; c.stage = M.stage; c.hist = M.hist; c.sm = M.sm;
+  c.cap = P.cap; c.keep = P.keep; c.mode = mode; c.k = rc.k_eff; c.logm = rc.logm;
   if (tid == 0) {
-    sm.n = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.best = 0ull; sm.gbest = 0ull; sm.smin = 0u;
+    sm.n = 0; sm.m = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.best = 0ull; sm.gbest = 0ull;
+    sm.smin = 0u;
   }
   __syncthreads();
   unsigned long long g = 0ull;
@@ -720,7 +875,7 @@ __global__ void __launch_bounds__(512) finish_candidates_kernel(const KParams P)
     if (lane == 0) atomicMax(&sm.best, a);
     __syncthreads();
   }
-  if (!failed && mode >= M_SELECT_K) {
+  if (!failed && (mode == M_SELECT_K || mode == M_SELECT_MINP)) {
     const int total_slots = parts * cap;
     for (int base = 0; base < total_slots; base += nt) {
       int i = base + tid;
@@ -732,20 +887,18 @@ __global__ void __launch_bounds__(512) finish_candidates_kernel(const KParams P)
         key = make_key(P.g_value[at], (uint32_t)P.g_id[at]);
         want = true;
       }
-      buffer_push(buf, hist, sm, P.cap, P.keep, mode, rc.k_eff, rc.logm, want, key);
+      buffer_push(c, want, key);
       if (sm.overflow) break;
     }
     __syncthreads();
-    if (!sm.overflow && (mode == M_SELECT_MINP || sm.n > rc.k_eff))
-      buffer_rebuild(buf, hist, sm, P.cap, P.keep, mode, rc.k_eff, rc.logm);
+    if (!sm.overflow && (mode == M_SELECT_MINP || sm.n > rc.k_eff)) buffer_rebuild(c);
     failed = sm.overflow != 0;
   }
   __syncthreads();
   if (failed || mode < M_SELECT_K) {
     KParams Q = P;
     Q.ws_flag = nullptr;
-    finish_simple(Q, rc, b, mode, sm.best, sm.gbest, failed);
-    clear_probs(P, b);
+    finish_simple(Q, b, mode, sm.best, sm.gbest, failed);
     return;
   }
   // the smallest score of the whole row is not gathered: with min_p alone the cut reported is

@@ -117,4 +117,3 @@ def test_config4_draft_verification(sampler, device):
                                             want.ids.reshape(n, drafts + 1))  # fmt: skip
     np.testing.assert_array_equal(accepted.cpu().numpy(), kept)
     np.testing.assert_array_equal(tokens.cpu().numpy(), toks)
-    assert kept.max() > 0  # the boosted drafts are accepted somewhere
