@@ -4,9 +4,11 @@ library is missing, importing this module raises."""
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
-LIBRARY = Path(__file__).resolve().parent / "csrc" / "libleat_sampler.so"
+# the in-tree build, unless LEAT_SAMPLER_LIBRARY names another build of the same sources
+LIBRARY = Path(os.environ.get("LEAT_SAMPLER_LIBRARY") or Path(__file__).resolve().parent / "csrc" / "libleat_sampler.so")
 
 OK, E_ARGUMENT, E_CAPACITY, E_WORKSPACE, E_CUDA, E_DEVICE = 0, -1, -2, -3, -4, -5
 STATUS_FALLBACK, STATUS_TRUNCATED, STATUS_INTERNAL = 1, 2, 4

@@ -74,7 +74,7 @@ struct Plan {
 size_t shared_bytes(int cap, int keep, int bm_words, int ht_size) {
   size_t stream = (size_t)bm_words * 4 + (size_t)ht_size * 8;
   size_t finish = (size_t)cap * 8 + (size_t)(cap / 32) * 4;
-  return (size_t)cap * 8 + (size_t)keep * 8 + (size_t)(BINS + 32) * 4 + 128 + (stream > finish ? stream : finish);
+  return (size_t)cap * 8 + (size_t)keep * 8 + (size_t)(BINS + 32) * 4 + SMEM_FIXED + (stream > finish ? stream : finish);
 }
 
 Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool has_history, int vec) {
@@ -311,10 +311,17 @@ int leat_sample_from_candidates(leat_sampler_t* h, const leat_sample_args* a, co
                                 const int32_t* cand_id, const int32_t* cand_count, const uint64_t* best,
                                 int32_t parts, int32_t cap, leat_stream_t stream) {
   if (!cand_value || !cand_id || !cand_count || !best || cap <= 0 || parts <= 0) return LEAT_E_ARGUMENT;
+  if (!h || !a) return LEAT_E_ARGUMENT;
+  // the handle is sized for this rank's slice; here `vocab` is the whole vocabulary's size
+  leat_sample_args whole = *a;
+  const int vocab = a->vocab_total > 0 ? a->vocab_total : a->vocab;
+  whole.vocab = 1;
+  whole.vocab_total = 0;
   KParams P;
-  int rc = fill_params(h, a, P);
+  int rc = fill_params(h, &whole, P);
   if (rc != LEAT_OK) return rc;
-  if (!a->out_ids) return LEAT_E_ARGUMENT;
+  if (!a->out_ids || vocab <= 0) return LEAT_E_ARGUMENT;
+  P.vocab = vocab; P.vocab_total = vocab;
   h->launches = 0;
   if (P.rows == 0) return LEAT_OK;
   int dev = -1;
@@ -329,5 +336,17 @@ int leat_sample_from_candidates(leat_sampler_t* h, const leat_sample_args* a, co
   h->launches = 1;
   return LEAT_OK;
 }
+
+#ifdef LEAT_PHASE_CLOCKS
+// development build only: cycles spent per phase, summed over blocks; clear != 0 zeroes them
+int leat_debug_phases(unsigned long long* out, int clear) {
+  if (out && cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 16) != cudaSuccess) return -1;
+  if (clear) {
+    unsigned long long zero[16] = {0};
+    if (cudaMemcpyToSymbol(g_phase_cycles, zero, sizeof(zero)) != cudaSuccess) return -1;
+  }
+  return 0;
+}
+#endif
 
 }  // extern "C"

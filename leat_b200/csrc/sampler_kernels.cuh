@@ -22,6 +22,15 @@
 
 namespace leat {
 
+#ifdef LEAT_PHASE_CLOCKS
+__device__ unsigned long long g_phase_cycles[16];
+#define PHASE_MARK(i) do { __syncthreads(); if (threadIdx.x == 0) { long long now_ = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(now_ - phase_t0_)); phase_t0_ = now_; } } while (0)
+#define PHASE_BEGIN() long long phase_t0_ = clock64()
+#else
+#define PHASE_MARK(i) do { } while (0)
+#define PHASE_BEGIN() do { } while (0)
+#endif
+
 enum RowMode : int {
   M_ARGMAX_L = 0,     // greedy: first argmax of the penalised logits
   M_ARGMAX_G = 1,     // no cut set, hashed draw: first argmax of score + gumbel over the whole row
@@ -32,6 +41,7 @@ enum RowMode : int {
 
 constexpr int UNROLL = 4;  // vectors per thread per streaming step
 constexpr int BINS = 2048;  // buckets of one select step
+constexpr int SMEM_FIXED = 384;  // Shared, Ctx and RowCfg, 128 bytes each
 constexpr int HASH_EMPTY = -1;
 constexpr int NO_ID = 0x7FFFFFFF;
 constexpr float GUMBEL_MAX = 17.0f;  // above -log(-log(1 - 2^-24)) = 16.64
@@ -71,6 +81,8 @@ struct RowCfg {
 
 struct Shared {
   int n;         // entries in the buffer (may run past cap until the next rebuild)
+  int conv;      // entries [0, conv) are (score, id) keys; the rest may be raw (logit, index) pairs
+  int valid;     // live entries counted by a rebuild
   int m;         // entries staged by a rebuild
   float tau;     // running threshold on scores
   int overflow;  // the slice / row cannot be reduced to `keep` candidates
@@ -91,6 +103,10 @@ struct Ctx {
   Shared* sm;
   int cap, keep, mode, k;
   float logm;
+  // raw appends: the stream stores (logit bits, index) and the rebuild turns them into keys
+  int divide, off, begin;
+  float rinv, tf;
+  const unsigned* bitmap;  // history tokens of the slice (their raw entries are dropped), or null
 };
 
 __device__ __forceinline__ float penalised(float l, int count, const RowCfg& rc) {
@@ -172,31 +188,59 @@ __device__ __forceinline__ bool warp_append(unsigned long long* dst, int* counte
 // entries span, then over the bucket that holds the k-th largest, until few enough remain (the
 // k-th largest itself at the finest step).  M_SELECT_MINP: the largest score held plus log(min_p).
 // Every entry at or above the threshold stays; sm.tau becomes the threshold.
-__device__ __noinline__ void buffer_rebuild(Ctx c) {
+__device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
   Shared& sm = *c.sm;
   unsigned long long* buf = c.buf;
   unsigned* hist = c.hist;
   unsigned* wtot = c.hist + BINS;
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
   const int n = min(sm.n, c.cap);
-  if (tid == 0) { sm.vmin = 0xFFFFFFFFu; sm.vmax = 0u; sm.m = 0; }
+  if (raw) {
+    // entries appended by the stream since the last rebuild are (logit, index): make them keys;
+    // a history token's raw logit is dropped (the history pass gave its penalised one), and so is
+    // anything below the threshold it was appended under
+    const float tau = sm.tau;
+    for (int i = sm.conv + tid; i < n; i += nt) {
+      const unsigned long long raw = buf[i];
+      const float l = __uint_as_float((uint32_t)(raw >> 32));
+      const int idx = (int)(uint32_t)raw;
+      bool drop = false;
+      if (c.bitmap) {
+        const int local = idx - c.begin;
+        drop = (c.bitmap[local >> 5] >> (local & 31)) & 1u;
+      }
+      const float sc = c.divide ? l / c.tf : l * c.rinv;
+      if (!(sc >= tau)) drop = true;
+      buf[i] = drop ? 0ull : make_key(sc, (uint32_t)(idx + c.off));
+    }
+  }
+  if (tid == 0) { sm.vmin = 0xFFFFFFFFu; sm.vmax = 0u; sm.m = 0; sm.valid = 0; }
   __syncthreads();
   {
     uint32_t mx = 0u, mn = 0xFFFFFFFFu;
+    int live = 0;
     for (int i = tid; i < n; i += nt) {
-      uint32_t v = key_vbits(buf[i]);
-      mx = max(mx, v);
-      mn = min(mn, v);
+      const unsigned long long key = buf[i];
+      if (key) {
+        uint32_t v = key_vbits(key);
+        mx = max(mx, v);
+        mn = min(mn, v);
+        live += 1;
+      }
     }
     mx = __reduce_max_sync(FULL, mx);
     mn = __reduce_min_sync(FULL, mn);
-    if (lane == 0) { atomicMax(&sm.vmax, mx); atomicMin(&sm.vmin, mn); }
+    live = __reduce_add_sync(FULL, live);
+    if (lane == 0) { atomicMax(&sm.vmax, mx); atomicMin(&sm.vmin, mn); atomicAdd(&sm.valid, live); }
   }
   __syncthreads();
-  uint32_t thr = 0u;
-  if (c.mode == M_SELECT_MINP) {
+  const int live = sm.valid;
+  uint32_t thr = 1u;  // every live entry (key bits of any score exceed 0)
+  if (live == 0) {
+    thr = 1u;
+  } else if (c.mode == M_SELECT_MINP) {
     thr = ord32(unord32(sm.vmax) + c.logm + 0.0f);
-  } else if (n > c.k) {
+  } else if (live > c.k) {
     uint32_t lo = sm.vmin, hi = sm.vmax;  // the k-th largest lies in [lo, hi]
     unsigned above = 0u;                  // entries above hi
     unsigned rem = (unsigned)c.k;         // the one sought is the rem-th largest within [lo, hi]
@@ -209,8 +253,9 @@ __device__ __noinline__ void buffer_rebuild(Ctx c) {
       for (int i = tid; i < BINS; i += nt) hist[i] = 0u;
       __syncthreads();
       for (int i = tid; i < n; i += nt) {
-        uint32_t v = key_vbits(buf[i]);
-        if (v >= lo && v <= hi) atomicAdd(&hist[(v - lo) >> shift], 1u);
+        const unsigned long long key = buf[i];
+        uint32_t v = key_vbits(key);
+        if (key && v >= lo && v <= hi) atomicAdd(&hist[(v - lo) >> shift], 1u);
       }
       __syncthreads();
       // thread t owns buckets BINS-1 - t*per - j, j < per: highest first
@@ -250,37 +295,33 @@ __device__ __noinline__ void buffer_rebuild(Ctx c) {
       (void)nwarps;
     }
   }
-  if (thr != 0u) {
-    // survivors go to the staging area, then back to the front of the buffer
-    for (int base = 0; base < n; base += nt) {
-      int i = base + tid;
-      unsigned long long key = (i < n) ? buf[i] : 0ull;
-      warp_append(c.stage, &sm.m, c.keep, i < n && key_vbits(key) >= thr, key);
-    }
-    __syncthreads();
-    const int m = min(sm.m, c.keep);
-    for (int i = tid; i < m; i += nt) buf[i] = c.stage[i];
-    if (tid == 0) {
-      if (sm.m > c.keep) sm.overflow = 1;
-      sm.n = m;
-      sm.tau = fmaxf(sm.tau, unord32(thr));
-    }
-  } else if (tid == 0) {
-    sm.n = n;
-    if (n >= c.cap) sm.overflow = 1;  // cannot happen while cap > k
+  // survivors go to the staging area, then back to the front of the buffer
+  for (int base = 0; base < n; base += nt) {
+    int i = base + tid;
+    unsigned long long key = (i < n) ? buf[i] : 0ull;
+    warp_append(c.stage, &sm.m, c.keep, key != 0ull && key_vbits(key) >= thr, key);
+  }
+  __syncthreads();
+  const int m = min(sm.m, c.keep);
+  for (int i = tid; i < m; i += nt) buf[i] = c.stage[i];
+  if (tid == 0) {
+    if (sm.m > c.keep) sm.overflow = 1;
+    sm.n = m;
+    sm.conv = m;
+    if (thr > 1u) sm.tau = fmaxf(sm.tau, unord32(thr));
   }
   __syncthreads();
 }
 
 // Block-synchronous append of one optional entry per thread (the merge of a row's slices).
-__device__ inline void buffer_push(Ctx c, bool want, unsigned long long key) {
+__device__ inline void buffer_push(const Ctx& c, bool want, unsigned long long key) {
   Shared& sm = *c.sm;
   bool pending = want && key_value(key) >= sm.tau;
   while (true) {
     bool ok = warp_append(c.buf, &sm.n, c.cap, pending, key);
     pending = pending && !ok;
     if (!__syncthreads_or(pending ? 1 : 0)) break;
-    buffer_rebuild(c);
+    buffer_rebuild(c, 0);
     if (sm.overflow) break;
     pending = pending && key_value(key) >= sm.tau;
   }
@@ -495,10 +536,117 @@ struct Tracked {
   float mns;          // smallest score among penalised elements
 };
 
+// The hot loop of top-k rows: [from, end) of one row against a running threshold.  A thread
+// compares its sixteen raw logits with a floor under which no logit can reach the threshold score;
+// the few at or above it are appended as raw (logit, index) pairs, which the next rebuild turns
+// into (score, id) keys (dropping history tokens, whose penalised logits came from the history
+// pass).  One barrier per step tells the block whether an append ran out of buffer.
+template <int VEC, bool PEN>
+__device__ __forceinline__ void stream_top_k(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
+                                             const float* __restrict__ row,
+                                             const uint8_t* __restrict__ seen_row, int from, int end,
+                                             Tracked& t) {
+  Shared& sm = *c.sm;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  constexpr int N = UNROLL * VEC;
+  if (tid == 0) sm.conv = sm.n;  // everything appended so far is a key
+  __syncthreads();
+  float floor_l = logit_floor(sm.tau, rc.tf);
+  bool stop = sm.overflow != 0;
+  const int stride = nt * VEC;
+  const int span = stride * UNROLL;
+  Chunk<VEC> cur, nxt;
+  if (!stop) load_chunk<VEC, PEN>(cur, row, seen_row, from + tid * VEC, stride, end);
+  for (int base = from; base < end && !stop; base += span) {
+    const int first = base + tid * VEC;
+    if (base + span < end) load_chunk<VEC, PEN>(nxt, row, seen_row, first + span, stride, end);
+    unsigned pm = 0u;  // logits at or above the floor
+    unsigned xm = 0u;  // elements under a dense seen mask: penalised one by one
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      if (PEN && cur.seen[u]) {
+        xm |= ((1u << VEC) - 1u) << (u * VEC);
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          if (cur.v[u * VEC + e] >= floor_l) pm |= 1u << (u * VEC + e);
+      }
+    }
+    if (rc.track) {
+      float m = neg_inf();
+#pragma unroll
+      for (int q = 0; q < N; ++q)
+        if (!((xm >> q) & 1u)) m = fmaxf(m, cur.v[q]);
+      if (m > t.gl) {
+#pragma unroll
+        for (int q = 0; q < N; ++q) {
+          const int idx = first + (q / VEC) * stride + (q % VEC);
+          const float l = cur.v[q];
+          if (l > t.gl && !((xm >> q) & 1u)) {
+            bool penalised_elsewhere = false;
+            if (PEN && P.history) {
+              const int local = idx - h.begin;
+              penalised_elsewhere = (h.bitmap[local >> 5] >> (local & 31)) & 1u;
+            }
+            if (!penalised_elsewhere) { t.gl = l; t.gid = idx; }
+          }
+        }
+      }
+    }
+    int rounds = 0;
+    while (true) {
+      unsigned redo = 0u, xredo = 0u;
+      if (PEN) {
+        while (__any_sync(FULL, xm != 0u)) {
+          const bool have = xm != 0u;
+          const int q = have ? __ffs(xm) - 1 : 0;
+          xm &= xm - 1u;
+          const int idx = first + (q / VEC) * stride + (q % VEC);
+          if (have && idx < end) {
+            const float l = exact_logit<PEN>(P, rc, h, seen_row, idx, pick(cur.v, q));
+            if (rc.track && (l > t.gl || (l == t.gl && idx < t.gid))) { t.gl = l; t.gid = idx; }
+            if (l >= floor_l) {
+              const int slot = atomicAdd(&sm.n, 1);
+              if (slot < c.cap) c.buf[slot] = ((unsigned long long)__float_as_uint(l) << 32) | (uint32_t)idx;
+              else xredo |= 1u << q;
+            }
+          }
+        }
+      }
+      if (__any_sync(FULL, pm != 0u)) {
+#pragma unroll
+        for (int q = 0; q < N; ++q) {
+          if ((pm >> q) & 1u) {
+            const int idx = first + (q / VEC) * stride + (q % VEC);
+            const int slot = atomicAdd(&sm.n, 1);
+            if (slot < c.cap) c.buf[slot] = ((unsigned long long)__float_as_uint(cur.v[q]) << 32) | (uint32_t)idx;
+            else redo |= 1u << q;
+          }
+        }
+      }
+      // one barrier per step: did any thread run out of buffer?
+      if (!__syncthreads_or((redo | xredo) != 0u)) break;
+      buffer_rebuild(c, 1);
+      floor_l = logit_floor(sm.tau, rc.tf);
+      if (sm.overflow || ++rounds > 64) {
+        if (tid == 0) sm.overflow = 1;
+        stop = true;
+        break;
+      }
+      pm = 0u;
+#pragma unroll
+      for (int q = 0; q < N; ++q)
+        if (((redo >> q) & 1u) && cur.v[q] >= floor_l) pm |= 1u << q;
+      xm = xredo;
+    }
+    cur = nxt;
+  }
+}
+
 // Streams [begin, end) of one row.  MODE is the row's mode; every warp of the block runs this with
 // the same arguments.
 template <int VEC, bool PEN, int MODE>
-__device__ __forceinline__ void stream_slice(const KParams& P, const RowCfg& rc, Ctx c, const History& h,
+__device__ __forceinline__ void stream_slice(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
                                              const float* __restrict__ row,
                                              const uint8_t* __restrict__ seen_row, int begin, int end,
                                              Tracked& t) {
@@ -506,6 +654,7 @@ __device__ __forceinline__ void stream_slice(const KParams& P, const RowCfg& rc,
   const int tid = threadIdx.x, nt = blockDim.x;
   const int off = P.vocab_offset;
   constexpr bool SELECT = (MODE == M_SELECT_K || MODE == M_SELECT_MINP);
+  PHASE_BEGIN();
   int from = begin;
   if (SELECT) {
     // the first `cap` elements go straight into the buffer
@@ -521,8 +670,43 @@ __device__ __forceinline__ void stream_slice(const KParams& P, const RowCfg& rc,
     __syncthreads();
     if (tid == 0) sm.n = fill_end - begin;
     __syncthreads();
-    if (end > fill_end) buffer_rebuild(c);
+    if (end > fill_end) buffer_rebuild(c, 0);
     from = fill_end;
+  }
+  PHASE_MARK(1);
+  if (PEN && P.history) {
+    // the penalised tokens of this slice come from the history table, not from the stream: one
+    // scattered load each, so the hot loop below never sees a penalised logit
+    for (int base = 0; base < h.mask + 1; base += nt) {
+      const int slot = base + tid;
+      const int idx = (slot <= h.mask) ? h.keys[slot] : HASH_EMPTY;
+      bool want = false;
+      unsigned long long key = 0ull;
+      if (idx != HASH_EMPTY && idx >= from && idx < end) {
+        int count = h.counts[slot];
+        if (seen_row && seen_row[idx]) count = max(count, 1);
+        float l = penalised(row[idx], count, rc);
+        if (rc.track && (l > t.gl || (l == t.gl && idx < t.gid))) { t.gl = l; t.gid = idx; }
+        float s = scaled(l, rc);
+        if (MODE == M_SELECT_MINP) t.mns = fminf(t.mns, s);
+        if (MODE == M_ARGMAX_G) {
+          float d = s + gumbel(hashed_uniform((uint32_t)(idx + off), rc.rkey));
+          if (d > t.al || (d == t.al && idx < t.aid)) { t.al = d; t.aid = idx; }
+        }
+        want = s == s;
+        key = make_key(s, (uint32_t)(idx + off));
+      }
+      if (SELECT) {
+        buffer_push(c, want, key);
+        if (sm.overflow) break;
+      }
+    }
+  }
+  PHASE_MARK(2);
+  if (MODE == M_SELECT_K) {
+    stream_top_k<VEC, PEN>(P, rc, c, h, row, seen_row, from, end, t);
+    PHASE_MARK(3);
+    return;
   }
   float tau = sm.tau;
   float floor_l = logit_floor(tau, rc.tf);
@@ -534,16 +718,25 @@ __device__ __forceinline__ void stream_slice(const KParams& P, const RowCfg& rc,
   for (int base = from; base < end && !stop; base += span) {
     const int first = base + tid * VEC;
     if (base + span < end) load_chunk<VEC, PEN>(nxt, row, seen_row, first + span, stride, end);
-    unsigned pm = 0u;  // elements that need the exact path
+    unsigned pm = 0u;    // elements that need the exact path
+    unsigned redo = 0u;  // elements whose entry did not fit the buffer
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int idx = first + u * stride;
-      unsigned flagged = 0u;
+      unsigned flagged = 0u;  // seen bytes of this vector: its elements take the exact path
       if (PEN) {
         if (idx < end) {
-          int local = idx - begin;
-          if (P.history) flagged = (h.bitmap[local >> 5] >> (local & 31)) & ((1u << VEC) - 1u);
-          flagged |= cur.seen[u];
+          if (P.history) {
+            // history tokens were handled from the table: blank them here
+            const int local = idx - begin;
+            const unsigned hb = (h.bitmap[local >> 5] >> (local & 31)) & ((1u << VEC) - 1u);
+            if (hb) {
+#pragma unroll
+              for (int e = 0; e < VEC; ++e)
+                if ((hb >> e) & 1u) cur.v[u * VEC + e] = quiet_nan();
+            }
+          }
+          flagged = cur.seen[u];
         }
       }
       if (PEN && flagged) {
@@ -556,29 +749,43 @@ __device__ __forceinline__ void stream_slice(const KParams& P, const RowCfg& rc,
 #pragma unroll
           for (int e = 0; e < VEC; ++e) t.mnl = fminf(t.mnl, cur.v[u * VEC + e]);
         }
+        if (rc.track && m4 > t.gl) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            float l = cur.v[u * VEC + e];
+            if (l > t.gl) { t.gl = l; t.gid = idx + e; }
+          }
+        }
         if (MODE == M_ARGMAX_G) {
           // score + gumbel can only win if score + the largest gumbel reaches the best so far
-          if (scaled(m4, rc) + GUMBEL_MAX >= t.al) pm |= ((1u << VEC) - 1u) << (u * VEC);
-          if (rc.track && m4 > t.gl) pm |= ((1u << VEC) - 1u) << (u * VEC);
-        } else {
-          if (rc.track && m4 > t.gl) {
+          if (scaled(m4, rc) + GUMBEL_MAX >= t.al) {
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
-              float l = cur.v[u * VEC + e];
-              if (l > t.gl) { t.gl = l; t.gid = idx + e; }
+              float sc = scaled(cur.v[u * VEC + e], rc);
+              if (sc + GUMBEL_MAX >= t.al) {
+                float d = sc + gumbel(hashed_uniform((uint32_t)(idx + e + off), rc.rkey));
+                if (d > t.al) { t.al = d; t.aid = idx + e; }
+              }
             }
           }
-          if (SELECT && m4 >= floor_l) {
+        } else if (SELECT && m4 >= floor_l) {
 #pragma unroll
-            for (int e = 0; e < VEC; ++e)
-              if (cur.v[u * VEC + e] >= floor_l) pm |= 1u << (u * VEC + e);
+          for (int e = 0; e < VEC; ++e) {
+            float l = cur.v[u * VEC + e];
+            if (l >= floor_l) {
+              float sc = scaled(l, rc);
+              if (sc >= tau) {
+                int slot = atomicAdd(&sm.n, 1);
+                if (slot < c.cap) c.buf[slot] = make_key(sc, (uint32_t)(idx + e + off));
+                else redo |= 1u << (u * VEC + e);
+              }
+            }
           }
         }
       }
     }
     // the exact path, one element per lane per round; an element whose entry does not fit is
     // redone after the block has rebuilt the buffer
-    unsigned redo = 0u;
     int rounds = 0;
     while (true) {
       while (__any_sync(FULL, pm != 0u)) {
@@ -611,7 +818,7 @@ __device__ __forceinline__ void stream_slice(const KParams& P, const RowCfg& rc,
       if (!SELECT) break;
       // one barrier per step: did any warp run out of buffer?
       if (!__syncthreads_or(redo != 0u)) break;
-      buffer_rebuild(c);
+      buffer_rebuild(c, 0);
       tau = sm.tau;
       floor_l = logit_floor(tau, rc.tf);
       if (sm.overflow || ++rounds > 64) {
@@ -624,6 +831,7 @@ __device__ __forceinline__ void stream_slice(const KParams& P, const RowCfg& rc,
     }
     cur = nxt;
   }
+  PHASE_MARK(3);
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
@@ -633,6 +841,8 @@ struct SmemMap {
   unsigned long long* stage;
   unsigned* hist;
   Shared* sm;
+  Ctx* ctx;
+  RowCfg* rc;
   unsigned char* region;  // streaming: bitmap + hash table; finishing: float scratch
 };
 
@@ -641,11 +851,14 @@ __device__ __forceinline__ SmemMap smem_map(unsigned char* raw, int cap, int kee
   m.buf = reinterpret_cast<unsigned long long*>(raw);
   m.stage = m.buf + cap;
   m.hist = reinterpret_cast<unsigned*>(m.stage + keep);
-  m.sm = reinterpret_cast<Shared*>(m.hist + BINS + 32);
-  m.region = reinterpret_cast<unsigned char*>(m.hist + BINS + 32) + 128;
+  unsigned char* at = reinterpret_cast<unsigned char*>(m.hist + BINS + 32);
+  m.sm = reinterpret_cast<Shared*>(at);
+  m.ctx = reinterpret_cast<Ctx*>(at + 128);
+  m.rc = reinterpret_cast<RowCfg*>(at + 256);
+  m.region = at + SMEM_FIXED;
   return m;
 }
-static_assert(sizeof(Shared) <= 128, "Shared must fit its slot");
+static_assert(sizeof(Shared) <= 128 && sizeof(Ctx) <= 128 && sizeof(RowCfg) <= 128, "slots of 128 bytes");
 
 template <int VEC, bool PEN>
 __global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
@@ -662,18 +875,26 @@ __global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
 
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
   const int b = blockIdx.y, slice = blockIdx.x, S = P.slices;
-  const RowCfg rc = row_config(P, b);
-  const int mode = rc.mode;
+  PHASE_BEGIN();
   const int begin = slice * P.slice_len;
   const int end = min(P.vocab, begin + P.slice_len);
   const float* row = P.logits + (size_t)b * P.row_stride;
   const uint8_t* seen_row = (PEN && P.seen) ? P.seen + (size_t)b * P.seen_stride : nullptr;
-  Ctx c;
-  c.buf = buf; c.stage = M.stage; c.hist = M.hist; c.sm = M.sm;
-  c.cap = P.cap; c.keep = P.keep; c.mode = mode; c.k = rc.k_eff; c.logm = rc.logm;
+  // the row's options and the buffer's description live in shared memory, not in registers
+  RowCfg& rc = *M.rc;
+  Ctx& c = *M.ctx;
+  if (tid == 0) {
+    rc = row_config(P, b);
+    c.buf = buf; c.stage = M.stage; c.hist = M.hist; c.sm = M.sm;
+    c.cap = P.cap; c.keep = P.keep; c.mode = rc.mode; c.k = rc.k_eff; c.logm = rc.logm;
+    c.divide = rc.divide; c.off = P.vocab_offset; c.begin = begin; c.rinv = rc.rinv; c.tf = rc.tf;
+    c.bitmap = (PEN && P.history) ? bitmap : nullptr;
+  }
+  __syncthreads();
+  const int mode = rc.mode;
 
   if (tid == 0) {
-    sm.n = 0; sm.m = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.best = 0ull; sm.gbest = 0ull;
+    sm.n = 0; sm.m = 0; sm.conv = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.best = 0ull; sm.gbest = 0ull;
     sm.smin = 0xFFFFFFFFu; sm.is_last = (S == 1);
   }
   History h;
@@ -702,6 +923,7 @@ __global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
     __syncthreads();
   }
 
+  PHASE_MARK(0);
   // ---- stream the slice once ----
   Tracked t;
   t.gl = neg_inf(); t.gid = NO_ID; t.al = neg_inf(); t.aid = NO_ID;
@@ -712,6 +934,9 @@ __global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
   else if (mode == M_SELECT_MINP) stream_slice<VEC, PEN, M_SELECT_MINP>(P, rc, c, h, row, seen_row, begin, end, t);
   __syncthreads();
 
+#ifdef LEAT_PHASE_CLOCKS
+  phase_t0_ = clock64();
+#endif
   // ---- reduce what the slice found ----
   if (rc.track) {
     unsigned long long g = (t.gid != NO_ID) ? make_key(t.gl, (uint32_t)(t.gid + P.vocab_offset)) : 0ull;
@@ -732,10 +957,12 @@ __global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
   }
   __syncthreads();
   if ((mode == M_SELECT_K || mode == M_SELECT_MINP) && !sm.overflow) {
-    if (mode == M_SELECT_MINP || sm.n > rc.k_eff) buffer_rebuild(c);
+    // the stream of a top-k row leaves raw entries behind: the rebuild also turns them into keys
+    if (mode == M_SELECT_MINP || sm.n > rc.k_eff || sm.conv < sm.n) buffer_rebuild(c, mode == M_SELECT_K);
   }
   bool failed = (mode == M_GENERAL) || sm.overflow;
 
+  PHASE_MARK(4);
   // ---- publish, and let the last block of the row go on ----
   if (S > 1) {
     const size_t cell = (size_t)b * S + slice;
@@ -760,8 +987,9 @@ __global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
     __syncthreads();
     if (!sm.is_last) return;
     __threadfence();
+    PHASE_MARK(5);
     // merge the row's slices
-    if (tid == 0) { sm.n = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.smin = 0xFFFFFFFFu; }
+    if (tid == 0) { sm.n = 0; sm.conv = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.smin = 0xFFFFFFFFu; }
     __syncthreads();
     unsigned long long g = 0ull, a = 0ull;
     unsigned mnb = 0xFFFFFFFFu;
@@ -794,12 +1022,13 @@ __global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
         if (sm.overflow) break;
       }
       __syncthreads();
-      if (!sm.overflow && (mode == M_SELECT_MINP || sm.n > rc.k_eff)) buffer_rebuild(c);
+      if (!sm.overflow && (mode == M_SELECT_MINP || sm.n > rc.k_eff)) buffer_rebuild(c, 0);
       failed = sm.overflow != 0;
     }
   }
   __syncthreads();
 
+  PHASE_MARK(6);
   // ---- the row is whole in this block ----
   if (P.cand_count) {  // shard mode: hand the row's candidates to the gather
     const int cap = P.cand_cap;
@@ -830,6 +1059,7 @@ __global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
     return;
   }
   finish_row(P, rc, b, buf, sm, fw, fi, fs, unord32(sm.smin));
+  PHASE_MARK(7);
 }
 
 // Finishes rows from candidates gathered from `g_parts` vocabulary slices: one block per row.
@@ -848,8 +1078,9 @@ __global__ void __launch_bounds__(512) finish_candidates_kernel(const KParams P)
   Ctx c;
   c.buf = buf; c.stage = M.stage; c.hist = M.hist; c.sm = M.sm;
   c.cap = P.cap; c.keep = P.keep; c.mode = mode; c.k = rc.k_eff; c.logm = rc.logm;
+  c.divide = 0; c.off = 0; c.begin = 0; c.rinv = 1.0f; c.tf = 1.0f; c.bitmap = nullptr;
   if (tid == 0) {
-    sm.n = 0; sm.m = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.best = 0ull; sm.gbest = 0ull;
+    sm.n = 0; sm.m = 0; sm.conv = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.best = 0ull; sm.gbest = 0ull;
     sm.smin = 0u;
   }
   __syncthreads();
@@ -891,7 +1122,7 @@ __global__ void __launch_bounds__(512) finish_candidates_kernel(const KParams P)
       if (sm.overflow) break;
     }
     __syncthreads();
-    if (!sm.overflow && (mode == M_SELECT_MINP || sm.n > rc.k_eff)) buffer_rebuild(c);
+    if (!sm.overflow && (mode == M_SELECT_MINP || sm.n > rc.k_eff)) buffer_rebuild(c, 0);
     failed = sm.overflow != 0;
   }
   __syncthreads();
