@@ -128,6 +128,20 @@ const char* leat_sampler_last_cuda_error(void);
    extensions the arguments describe. */
 int leat_sample(leat_sampler_t* handle, const leat_sample_args* args, leat_stream_t stream);
 
+/* leat_sample() without a handle or a workspace, for callers that cannot allocate device memory:
+   a server whose memory pool is already fully committed, a foreign-language binding that only
+   receives device pointers and owns no allocator, or a step that must not pay cudaMalloc's
+   device-wide synchronisation.  It has no counterpart in the reference (leat's kernels allocate
+   their scratch per call).  The scratch the blocks of a row exchange lives in a fixed array of
+   about 1.1 MB inside the library, held by every GPU that loads the library until the process
+   exits.  Limits: rows <= 64, vocab <= 262144, top_k <= 64 on the single-pass path; a larger call
+   returns LEAT_E_CAPACITY.  The caller still passes every input and output buffer.  The first call
+   on a device looks up the array's device address and raises the kernels' shared-memory limit,
+   so make that first call outside any stream capture.  All calls on a device share the one array:
+   calls that overlap on the GPU (different streams) race; issue them on one stream or order them.
+   Calls cudaMalloc, cudaFree or any allocating routine nowhere. */
+int leat_sample_static(const leat_sample_args* args, leat_stream_t stream);
+
 /* ops.argmax(): leat/ops.py:496-500 and leat/kernels/argmax.py:48-61.  x (rows, vocab) float32 ->
    out (rows,) int32, the first index of each row's largest value. */
 int leat_argmax(leat_sampler_t* handle, const float* x, int32_t rows, int32_t vocab,

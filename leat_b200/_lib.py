@@ -26,7 +26,7 @@ EXPORTS = [
     "leat_sampler_workspace_bytes", "leat_sampler_create", "leat_sampler_destroy",
     "leat_sampler_tune", "leat_sampler_plan", "leat_sampler_last_launches",
     "leat_sampler_last_cuda_error", "leat_sample", "leat_argmax", "leat_cutoff",
-    "leat_verify_draft", "leat_topk_local", "leat_sample_from_candidates",
+    "leat_verify_draft", "leat_topk_local", "leat_sample_from_candidates", "leat_sample_static",
 ]  # fmt: skip
 
 
@@ -71,6 +71,7 @@ def _load() -> C.CDLL:
     lib.leat_sampler_last_cuda_error.restype = C.c_char_p
     lib.leat_sampler_last_cuda_error.argtypes = []
     lib.leat_sample.argtypes = [p, C.POINTER(SampleArgs), p]
+    lib.leat_sample_static.argtypes = [C.POINTER(SampleArgs), p]
     lib.leat_argmax.argtypes = [p, p, i32, i32, i64, p, p, p]
     lib.leat_cutoff.argtypes = [p, p, i32, i32, i64, p, p, p, p, p, p]
     lib.leat_verify_draft.argtypes = [p, p, p, i32, i32, p, p, p]

@@ -337,6 +337,97 @@ int leat_sample_from_candidates(leat_sampler_t* h, const leat_sample_args* a, co
   return LEAT_OK;
 }
 
+// ---- sampling without any allocation -------------------------------------------------------------
+//
+// Some callers cannot hand the library a workspace because they cannot allocate device memory at
+// the point of the call at all: an inference server that has already given every free byte to its
+// KV-cache pool, a host binding (cgo, JNI, ctypes) that only ever receives device pointers from its
+// framework and has no allocator of its own, or a step running where cudaMalloc's implicit
+// device-wide synchronisation is not acceptable.  For them leat_sample_static() keeps the scratch
+// the slices of a row exchange in a fixed array inside the library's own device image.
+constexpr int kStaticRows = 64;
+constexpr int kStaticVocab = 1 << 18;
+constexpr int kStaticK = 64;
+constexpr int kStaticCells = 1024;  // blocks of one call: rows x slices
+
+constexpr size_t static_region(size_t bytes) { return (bytes + 255) / 256 * 256; }
+constexpr int kStaticKeep = (kStaticK + 64 + 63) / 64 * 64;
+constexpr size_t kStaticBytes = static_region((size_t)kStaticCells * kStaticKeep * 8) +
+                                static_region((size_t)kStaticCells * 4) + static_region((size_t)kStaticCells * 16) +
+                                static_region((size_t)kStaticCells * 4) + 2 * static_region((size_t)kStaticRows * 4);
+
+// Every GPU that loads the library holds this array (about 1.1 MB) until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+namespace {
+
+struct StaticDevice {
+  bool ready;
+  leat_sampler handle;
+};
+StaticDevice g_static_devices[64];
+
+// Once per device, with that device current: the array's name is only a host-side stand-in, so
+// ask the runtime for the device address kernels can use.
+int static_setup(int device, StaticDevice** out) {
+  if (device < 0 || device >= 64) return LEAT_E_DEVICE;
+  StaticDevice& sd = g_static_devices[device];
+  if (!sd.ready) {
+    void* scratch = nullptr;
+    if (cuda_failed(cudaGetSymbolAddress(&scratch, g_static_scratch), "cudaGetSymbolAddress")) return LEAT_E_CUDA;
+    leat_sampler& h = sd.handle;
+    h.device = device; h.max_rows = kStaticRows; h.max_vocab = kStaticVocab; h.k_max = kStaticK;
+    h.keep = keep_for(kStaticK); h.cap = cap_for(h.keep);
+    h.tune_threads = 0; h.tune_slices = 0; h.launches = 0;
+    Layout& L = h.L;
+    L.cells = kStaticCells;
+    size_t at = 0;
+    auto take = [&](size_t bytes) { size_t here = at; at += static_region(bytes); return here; };
+    L.keys = take((size_t)L.cells * h.keep * 8);
+    L.count = take((size_t)L.cells * 4);
+    L.best = take((size_t)L.cells * 16);
+    L.vmin = take((size_t)L.cells * 4);
+    L.ticket = take((size_t)kStaticRows * 4);
+    L.flag = take((size_t)kStaticRows * 4);
+    L.total = at;
+    if (L.total > kStaticBytes || h.keep != kStaticKeep) return LEAT_E_WORKSPACE;
+    h.ws = static_cast<unsigned char*>(scratch);
+    int sms = 0;
+    if (cuda_failed(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute"))
+      return LEAT_E_CUDA;
+    h.sm_count = sms > 0 ? sms : 148;
+    const int most = (int)shared_bytes(h.cap, h.keep, kMaxSliceLen / 32, 16384);
+    if (allow_shared(sample_kernel<4, true>, most) || allow_shared(sample_kernel<4, false>, most) ||
+        allow_shared(sample_kernel<1, true>, most) || allow_shared(sample_kernel<1, false>, most))
+      return LEAT_E_CUDA;
+    sd.ready = true;
+  }
+  *out = &sd;
+  return LEAT_OK;
+}
+
+}  // namespace
+
+int leat_sample_static(const leat_sample_args* a, leat_stream_t stream) {
+  if (!a || !a->out_ids) return LEAT_E_ARGUMENT;
+  if (a->rows > kStaticRows || a->vocab > kStaticVocab) return LEAT_E_CAPACITY;
+  int device = -1;
+  if (cuda_failed(cudaGetDevice(&device), "cudaGetDevice")) return LEAT_E_CUDA;
+  StaticDevice* sd = nullptr;
+  int rc = static_setup(device, &sd);
+  if (rc != LEAT_OK) return rc;
+  leat_sampler* h = &sd->handle;
+  KParams P;
+  rc = fill_params(h, a, P);
+  if (rc != LEAT_OK) return rc;
+  // the array keeps what the last call left: the words that count a row's finished slices and mark
+  // rows for the multi-pass kernel must start at zero
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cuda_failed(cudaMemsetAsync(h->ws + h->L.ticket, 0, h->L.total - h->L.ticket, s), "cudaMemsetAsync"))
+    return LEAT_E_CUDA;
+  return launch_sample(h, P, s);
+}
+
 #ifdef LEAT_PHASE_CLOCKS
 // development build only: cycles spent per phase, summed over blocks; clear != 0 zeroes them
 int leat_debug_phases(unsigned long long* out, int clear) {

@@ -250,6 +250,37 @@ def default_sampler(rows: int, vocab: int, device: torch.device, k_max: int = 25
     return have
 
 
+def sample_static(logits: torch.Tensor, options, seed=None, position=0, seen=None, *, history=None,
+                  history_len=None, penalties=None, uniform=None, width: int = 0, want_greedy: bool = False,
+                  flags: int = 0, out: torch.Tensor | None = None) -> Sampled:  # fmt: skip
+    """sample_full() through the library's allocation-free entry point (leat_sample_static): no
+    Sampler, no workspace -- the library keeps its scratch in a fixed array of its own.  For
+    callers that cannot allocate device memory where they sample.  Up to 64 rows, 262144 tokens and
+    top_k 64; all calls on a device share the scratch, so keep them on one stream.  (This Python
+    wrapper still creates its output tensors unless `out` is given; the C entry point itself
+    allocates nothing.)"""
+    a, keep = Sampler._args(None, logits, options, seed, position, seen, history, history_len, penalties,
+                            uniform, flags)  # fmt: skip
+    rows, dev = a.rows, logits.device
+    ids = out if out is not None else torch.empty((rows, 1), dtype=torch.int32, device=dev)
+    result = Sampled(ids, status=torch.zeros(1, dtype=torch.int32, device=dev))
+    a.out_ids, a.status = ids.data_ptr(), result.status.data_ptr()
+    if want_greedy:
+        result.greedy = torch.empty(rows, dtype=torch.int32, device=dev)
+        a.out_greedy = result.greedy.data_ptr()
+    if width:
+        result.cut = torch.empty(rows, dtype=torch.float32, device=dev)
+        result.kept = torch.empty(rows, dtype=torch.int32, device=dev)
+        result.probs = torch.empty((rows, width), dtype=torch.float32, device=dev)
+        result.prob_ids = torch.empty((rows, width), dtype=torch.int32, device=dev)
+        a.out_cut, a.out_kept = result.cut.data_ptr(), result.kept.data_ptr()
+        a.out_probs, a.out_prob_ids, a.out_width = result.probs.data_ptr(), result.prob_ids.data_ptr(), width
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib.leat_sample_static(C.byref(a), _stream()), "leat_sample_static")
+    del keep
+    return result
+
+
 def sample(logits: torch.Tensor, options: torch.Tensor, seed: torch.Tensor, position, seen=None,
            **extensions) -> torch.Tensor:  # fmt: skip
     """leat/sampler.py:31-55: picks one token per row of `logits` (B, V), as its options say;
