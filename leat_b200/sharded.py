@@ -73,10 +73,11 @@ class ShardedSampler:
         """One all-gather per array: every rank ends with every rank's candidates, part-major."""
         if rows != self.max_rows:
             raise ValueError("the gather buffers are sized for max_rows rows")
-        dist.all_gather_into_tensor(self.all_count, self.count, group=self.group)
-        dist.all_gather_into_tensor(self.all_value, self.value, group=self.group)
-        dist.all_gather_into_tensor(self.all_ids, self.ids, group=self.group)
-        dist.all_gather_into_tensor(self.all_best, self.best, group=self.group)
+        # outputs viewed as the inputs concatenated along their first axis (part-major)
+        dist.all_gather_into_tensor(self.all_count.view(-1), self.count, group=self.group)
+        dist.all_gather_into_tensor(self.all_value.view(-1, self.cap), self.value, group=self.group)
+        dist.all_gather_into_tensor(self.all_ids.view(-1, self.cap), self.ids, group=self.group)
+        dist.all_gather_into_tensor(self.all_best.view(-1), self.best, group=self.group)
 
     def finish(self, rows, options, seed, position, uniform=None, width: int = 0, flags: int = 0,
                out: torch.Tensor | None = None) -> Sampled:  # fmt: skip
