@@ -116,6 +116,9 @@ int leat_sampler_destroy(leat_sampler_t* handle);
 /* Launch shape override for experiments: threads per block (128, 256 or 512; 0 = automatic) and
    blocks per row (0 = automatic). */
 int leat_sampler_tune(leat_sampler_t* handle, int32_t threads, int32_t slices);
+/* Stages of the shared-memory ring the stream's bulk copies fill: 0 = automatic, 2..8 = that many,
+   negative = no ring (the stream loads into registers instead). */
+int leat_sampler_tune_ring(leat_sampler_t* handle, int32_t stages);
 /* The launch shape the handle would use for (rows, vocab): writes threads, slices, blocks. */
 int leat_sampler_plan(const leat_sampler_t* handle, int32_t rows, int32_t vocab, int32_t history_cap,
                       int32_t* threads, int32_t* slices, int32_t* shared_bytes);

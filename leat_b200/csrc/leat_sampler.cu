@@ -58,7 +58,7 @@ int cap_for(int keep) { return keep <= 512 ? 2048 : 4096; }
 
 struct leat_sampler {
   int device, max_rows, max_vocab, k_max, keep, cap;
-  int tune_threads, tune_slices;
+  int tune_threads, tune_slices, tune_stages, tune_no_ring;
   int sm_count;
   int launches;
   unsigned char* ws;
@@ -68,13 +68,21 @@ struct leat_sampler {
 namespace {
 
 struct Plan {
-  int vec, threads, slices, slice_len, bm_words, ht_size, shared;
+  int vec, threads, slices, slice_len, bm_words, ht_size, shared, ring_stages;
 };
 
-size_t shared_bytes(int cap, int keep, int bm_words, int ht_size) {
-  size_t stream = (size_t)bm_words * 4 + (size_t)ht_size * 8;
+constexpr size_t kSharedPerBlockTarget = 112 * 1024;  // two blocks per SM
+
+size_t fixed_shared(int cap, int keep) {
+  return (size_t)cap * 8 + (size_t)keep * 8 + (size_t)(BINS + 32) * 4 + SMEM_FIXED;
+}
+
+size_t shared_bytes(int cap, int keep, int bm_words, int ht_size, size_t ring = 0) {
+  size_t bitmap = ((size_t)bm_words * 4 + 127) / 128 * 128;
+  size_t table = (size_t)ht_size * 8;
+  size_t stream = bitmap + (table > ring ? table : ring);
   size_t finish = (size_t)cap * 8 + (size_t)(cap / 32) * 4;
-  return (size_t)cap * 8 + (size_t)keep * 8 + (size_t)(BINS + 32) * 4 + SMEM_FIXED + (stream > finish ? stream : finish);
+  return fixed_shared(cap, keep) + (stream > finish ? stream : finish);
 }
 
 Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool has_history, int vec) {
@@ -99,7 +107,17 @@ Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool
   if (p.slices < 1) p.slices = 1;
   p.bm_words = has_history ? p.slice_len / 32 : 0;
   p.ht_size = has_history ? next_pow2(history_cap * 2 < 64 ? 64 : history_cap * 2) : 0;
-  p.shared = (int)shared_bytes(h->cap, h->keep, p.bm_words, p.ht_size);
+  // the ring of bulk copies: as many stages as fit a block's share of shared memory
+  p.ring_stages = 0;
+  if (vec == 4 && !h->tune_no_ring) {
+    const size_t stage = (size_t)p.threads * 16 * 4;
+    const size_t used = fixed_shared(h->cap, h->keep) + ((size_t)p.bm_words * 4 + 127) / 128 * 128;
+    int stages = used < kSharedPerBlockTarget ? (int)((kSharedPerBlockTarget - used) / stage) : 0;
+    if (h->tune_stages) stages = h->tune_stages;
+    if (stages > MAX_RING_STAGES) stages = MAX_RING_STAGES;
+    if (stages >= 2) p.ring_stages = stages;
+  }
+  p.shared = (int)shared_bytes(h->cap, h->keep, p.bm_words, p.ht_size, (size_t)p.ring_stages * p.threads * 16 * 4);
   return p;
 }
 
@@ -167,6 +185,7 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
   const int vec = pick_vec(P);
   Plan plan = make_plan(h, P.rows, P.vocab, P.history_cap, P.history != nullptr, vec);
   P.slices = plan.slices; P.slice_len = plan.slice_len; P.bm_words = plan.bm_words; P.ht_size = plan.ht_size;
+  P.ring_stages = (P.seen == nullptr) ? plan.ring_stages : 0;
   int rc;
   if (vec == 4) rc = pen ? launch_one<4, true>(P, plan, stream) : launch_one<4, false>(P, plan, stream);
   else rc = pen ? launch_one<1, true>(P, plan, stream) : launch_one<1, false>(P, plan, stream);
@@ -197,7 +216,7 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
   if (!h) return LEAT_E_ARGUMENT;
   h->device = device; h->max_rows = max_rows; h->max_vocab = max_vocab; h->k_max = k_max;
   h->keep = keep_for(k_max); h->cap = cap_for(h->keep);
-  h->tune_threads = 0; h->tune_slices = 0; h->launches = 0;
+  h->tune_threads = 0; h->tune_slices = 0; h->tune_stages = 0; h->tune_no_ring = 0; h->launches = 0;
   h->L = layout_for(max_rows, max_vocab, h->keep);
   h->ws = static_cast<unsigned char*>(workspace);
   if (bytes < h->L.total || !aligned(workspace, 256)) { delete h; return LEAT_E_WORKSPACE; }
@@ -209,7 +228,7 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
     delete h; return LEAT_E_CUDA;
   }
   h->sm_count = sms > 0 ? sms : 148;
-  const int most = (int)shared_bytes(h->cap, h->keep, kMaxSliceLen / 32, 16384);
+  const int most = 200 * 1024;
   if (allow_shared(sample_kernel<4, true>, most) || allow_shared(sample_kernel<4, false>, most) ||
       allow_shared(sample_kernel<1, true>, most) || allow_shared(sample_kernel<1, false>, most) ||
       allow_shared(finish_candidates_kernel, most)) {
@@ -233,6 +252,13 @@ int leat_sampler_tune(leat_sampler_t* h, int32_t threads, int32_t slices) {
   if (threads != 0 && threads != 128 && threads != 256 && threads != 512) return LEAT_E_ARGUMENT;
   if (slices < 0) return LEAT_E_ARGUMENT;
   h->tune_threads = threads; h->tune_slices = slices;
+  return LEAT_OK;
+}
+
+int leat_sampler_tune_ring(leat_sampler_t* h, int32_t stages) {
+  if (!h || stages > MAX_RING_STAGES) return LEAT_E_ARGUMENT;
+  h->tune_no_ring = stages < 0 ? 1 : 0;
+  h->tune_stages = stages > 0 ? stages : 0;
   return LEAT_OK;
 }
 
@@ -378,7 +404,7 @@ int static_setup(int device, StaticDevice** out) {
     leat_sampler& h = sd.handle;
     h.device = device; h.max_rows = kStaticRows; h.max_vocab = kStaticVocab; h.k_max = kStaticK;
     h.keep = keep_for(kStaticK); h.cap = cap_for(h.keep);
-    h.tune_threads = 0; h.tune_slices = 0; h.launches = 0;
+    h.tune_threads = 0; h.tune_slices = 0; h.tune_stages = 0; h.tune_no_ring = 0; h.launches = 0;
     Layout& L = h.L;
     L.cells = kStaticCells;
     size_t at = 0;
@@ -396,7 +422,7 @@ int static_setup(int device, StaticDevice** out) {
     if (cuda_failed(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute"))
       return LEAT_E_CUDA;
     h.sm_count = sms > 0 ? sms : 148;
-    const int most = (int)shared_bytes(h.cap, h.keep, kMaxSliceLen / 32, 16384);
+    const int most = 200 * 1024;
     if (allow_shared(sample_kernel<4, true>, most) || allow_shared(sample_kernel<4, false>, most) ||
         allow_shared(sample_kernel<1, true>, most) || allow_shared(sample_kernel<1, false>, most))
       return LEAT_E_CUDA;

@@ -41,7 +41,8 @@ enum RowMode : int {
 
 constexpr int UNROLL = 4;  // vectors per thread per streaming step
 constexpr int BINS = 2048;  // buckets of one select step
-constexpr int SMEM_FIXED = 384;  // Shared, Ctx and RowCfg, 128 bytes each
+constexpr int SMEM_FIXED = 640;  // Shared (256 bytes), Ctx, RowCfg and the ring's mbarriers (128 bytes each)
+constexpr int MAX_RING_STAGES = 8;
 constexpr int HASH_EMPTY = -1;
 constexpr int NO_ID = 0x7FFFFFFF;
 constexpr float GUMBEL_MAX = 17.0f;  // above -log(-log(1 - 2^-24)) = 16.64
@@ -63,7 +64,7 @@ struct KParams {
   // gathered candidates (finish-from-candidates kernel)
   const float* g_value; const int* g_id; const int* g_count; const unsigned long long* g_best; int g_parts;
   // launch plan
-  int slices; int slice_len; int cap; int keep; int k_max; int bm_words; int ht_size;
+  int slices; int slice_len; int cap; int keep; int k_max; int bm_words; int ht_size; int ring_stages;
   // workspace
   unsigned long long* ws_keys;  // (rows, slices, keep)
   int* ws_count;                // (rows, slices): candidates published, -1 = could not reduce
@@ -93,6 +94,7 @@ struct Shared {
   unsigned long long gbest;  // block max of the greedy key
   unsigned smin;             // block min of score bits (ord32)
   int jstar, ns, pick;
+  int wcount[32];  // raw entries each warp holds in its own region of the buffer
 };
 
 // what the candidate buffer needs, by value in registers
@@ -105,6 +107,7 @@ struct Ctx {
   float logm;
   // raw appends: the stream stores (logit bits, index) and the rebuild turns them into keys
   int divide, off, begin;
+  int region;  // raw slots per warp, after the first `keep` slots of the buffer
   float rinv, tf;
   const unsigned* bitmap;  // history tokens of the slice (their raw entries are dropped), or null
 };
@@ -194,33 +197,35 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
   unsigned* hist = c.hist;
   unsigned* wtot = c.hist + BINS;
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
-  const int n = min(sm.n, c.cap);
-  if (raw) {
-    // entries appended by the stream since the last rebuild are (logit, index): make them keys;
-    // a history token's raw logit is dropped (the history pass gave its penalised one), and so is
-    // anything below the threshold it was appended under
-    const float tau = sm.tau;
-    for (int i = sm.conv + tid; i < n; i += nt) {
-      const unsigned long long raw = buf[i];
-      const float l = __uint_as_float((uint32_t)(raw >> 32));
-      const int idx = (int)(uint32_t)raw;
-      bool drop = false;
-      if (c.bitmap) {
-        const int local = idx - c.begin;
-        drop = (c.bitmap[local >> 5] >> (local & 31)) & 1u;
-      }
-      const float sc = c.divide ? l / c.tf : l * c.rinv;
-      if (!(sc >= tau)) drop = true;
-      buf[i] = drop ? 0ull : make_key(sc, (uint32_t)(idx + c.off));
-    }
-  }
+  // raw mode: slots [0, conv) hold keys, [conv, keep) are empty, and warp w's raw (logit, index)
+  // pairs sit in [keep + w * region, ... + wcount[w]); every other slot is taken as empty
+  const int region = c.region;
+  const int n = raw ? c.keep + nwarps * region : min(sm.n, c.cap);
   if (tid == 0) { sm.vmin = 0xFFFFFFFFu; sm.vmax = 0u; sm.m = 0; sm.valid = 0; }
   __syncthreads();
   {
+    const float tau = sm.tau;
     uint32_t mx = 0u, mn = 0xFFFFFFFFu;
     int live = 0;
     for (int i = tid; i < n; i += nt) {
-      const unsigned long long key = buf[i];
+      unsigned long long key = buf[i];
+      if (raw && i >= c.keep) {
+        // make a raw pair a key; a history token's raw logit is dropped (the history pass gave
+        // its penalised one), and so is anything below the threshold it was appended under
+        const int w = (i - c.keep) / region;
+        const bool held = (i - c.keep) - w * region < sm.wcount[w];
+        const float l = __uint_as_float((uint32_t)(key >> 32));
+        const int idx = (int)(uint32_t)key;
+        bool drop = !held;
+        if (held && c.bitmap) {
+          const int local = idx - c.begin;
+          drop = (c.bitmap[local >> 5] >> (local & 31)) & 1u;
+        }
+        const float sc = c.divide ? l / c.tf : l * c.rinv;
+        if (!(sc >= tau)) drop = true;
+        key = drop ? 0ull : make_key(sc, (uint32_t)(idx + c.off));
+        buf[i] = key;
+      }
       if (key) {
         uint32_t v = key_vbits(key);
         mx = max(mx, v);
@@ -286,7 +291,8 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
       __syncthreads();
       const uint32_t edge = lo + ((uint32_t)sm.sel_bin << shift);
       const unsigned at_or_above = above + (unsigned)sm.sel_above + (unsigned)sm.sel_count;
-      if (at_or_above <= (unsigned)c.keep || shift == 0) { thr = edge; break; }
+      // accept a threshold that keeps little more than k: a loose one lets too much through later
+      if (at_or_above <= (unsigned)min(c.keep, c.k + max(8, c.k >> 3)) || shift == 0) { thr = edge; break; }
       above += (unsigned)sm.sel_above;
       rem -= (unsigned)sm.sel_above;
       const uint32_t last = edge + ((1u << shift) - 1u);
@@ -303,7 +309,8 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
   }
   __syncthreads();
   const int m = min(sm.m, c.keep);
-  for (int i = tid; i < m; i += nt) buf[i] = c.stage[i];
+  for (int i = tid; i < c.keep; i += nt) buf[i] = (i < m) ? c.stage[i] : 0ull;
+  if (tid < 32) sm.wcount[tid] = 0;
   if (tid == 0) {
     if (sm.m > c.keep) sm.overflow = 1;
     sm.n = m;
@@ -542,15 +549,21 @@ struct Tracked {
 // into (score, id) keys (dropping history tokens, whose penalised logits came from the history
 // pass).  One barrier per step tells the block whether an append ran out of buffer.
 template <int VEC, bool PEN>
-__device__ __forceinline__ void stream_top_k(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
-                                             const float* __restrict__ row,
-                                             const uint8_t* __restrict__ seen_row, int from, int end,
-                                             Tracked& t) {
+__device__ __noinline__ void stream_top_k(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
+                                          const float* __restrict__ row, const uint8_t* __restrict__ seen_row,
+                                          int from, int end, Tracked& t) {
   Shared& sm = *c.sm;
-  const int tid = threadIdx.x, nt = blockDim.x;
+  const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
   constexpr int N = UNROLL * VEC;
-  if (tid == 0) sm.conv = sm.n;  // everything appended so far is a key
+  // keys so far fit the first `keep` slots; the rest of the buffer is one raw region per warp
+  if (sm.n > c.keep) buffer_rebuild(c, 0);
+  for (int i = sm.n + tid; i < c.keep; i += nt) c.buf[i] = 0ull;
+  if (tid < 32) sm.wcount[tid] = 0;
+  if (tid == 0) sm.conv = sm.n;
   __syncthreads();
+  const int region = c.region;
+  unsigned long long* const mine = c.buf + c.keep + warp * region;
+  int held = 0;  // raw entries in this warp's region (the same in every lane)
   float floor_l = logit_floor(sm.tau, rc.tf);
   bool stop = sm.overflow != 0;
   const int stride = nt * VEC;
@@ -602,31 +615,49 @@ __device__ __forceinline__ void stream_top_k(const KParams& P, const RowCfg& rc,
           const int q = have ? __ffs(xm) - 1 : 0;
           xm &= xm - 1u;
           const int idx = first + (q / VEC) * stride + (q % VEC);
+          bool want = false;
+          float l = 0.0f;
           if (have && idx < end) {
-            const float l = exact_logit<PEN>(P, rc, h, seen_row, idx, pick(cur.v, q));
+            l = exact_logit<PEN>(P, rc, h, seen_row, idx, pick(cur.v, q));
             if (rc.track && (l > t.gl || (l == t.gl && idx < t.gid))) { t.gl = l; t.gid = idx; }
-            if (l >= floor_l) {
-              const int slot = atomicAdd(&sm.n, 1);
-              if (slot < c.cap) c.buf[slot] = ((unsigned long long)__float_as_uint(l) << 32) | (uint32_t)idx;
-              else xredo |= 1u << q;
-            }
+            want = l >= floor_l;
           }
+          const unsigned mask = __ballot_sync(FULL, want);
+          if (want) {
+            const int slot = held + __popc(mask & ((1u << lane) - 1u));
+            if (slot < region) mine[slot] = ((unsigned long long)__float_as_uint(l) << 32) | (uint32_t)idx;
+            else xredo |= 1u << q;
+          }
+          held = min(held + __popc(mask), region);
         }
       }
       if (__any_sync(FULL, pm != 0u)) {
+        // the warp's passing logits go to its own region: no atomics, one scan over the lanes
+        const int count = __popc(pm);
+        int incl = count;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int o = __shfl_up_sync(FULL, incl, d);
+          if (lane >= d) incl += o;
+        }
+        const int total = __shfl_sync(FULL, incl, 31);
+        int slot = held + incl - count;
 #pragma unroll
         for (int q = 0; q < N; ++q) {
           if ((pm >> q) & 1u) {
             const int idx = first + (q / VEC) * stride + (q % VEC);
-            const int slot = atomicAdd(&sm.n, 1);
-            if (slot < c.cap) c.buf[slot] = ((unsigned long long)__float_as_uint(cur.v[q]) << 32) | (uint32_t)idx;
+            if (slot < region) mine[slot] = ((unsigned long long)__float_as_uint(cur.v[q]) << 32) | (uint32_t)idx;
             else redo |= 1u << q;
+            ++slot;
           }
         }
+        held = min(held + total, region);
       }
-      // one barrier per step: did any thread run out of buffer?
+      if (lane == 0) sm.wcount[warp] = held;
+      // one barrier per step: did any warp run out of room?
       if (!__syncthreads_or((redo | xredo) != 0u)) break;
       buffer_rebuild(c, 1);
+      held = 0;
       floor_l = logit_floor(sm.tau, rc.tf);
       if (sm.overflow || ++rounds > 64) {
         if (tid == 0) sm.overflow = 1;
@@ -643,13 +674,15 @@ __device__ __forceinline__ void stream_top_k(const KParams& P, const RowCfg& rc,
   }
 }
 
+#include "stream_ring.cuh"
+
 // Streams [begin, end) of one row.  MODE is the row's mode; every warp of the block runs this with
 // the same arguments.
 template <int VEC, bool PEN, int MODE>
 __device__ __forceinline__ void stream_slice(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
                                              const float* __restrict__ row,
                                              const uint8_t* __restrict__ seen_row, int begin, int end,
-                                             Tracked& t) {
+                                             Tracked& t, Ring ring) {
   Shared& sm = *c.sm;
   const int tid = threadIdx.x, nt = blockDim.x;
   const int off = P.vocab_offset;
@@ -703,6 +736,11 @@ __device__ __forceinline__ void stream_slice(const KParams& P, const RowCfg& rc,
     }
   }
   PHASE_MARK(2);
+  if (VEC == 4 && MODE != M_SELECT_MINP && ring.stages > 0 && seen_row == nullptr) {
+    stream_ring<PEN, MODE>(P, rc, c, h, row, from, end, t, ring);
+    PHASE_MARK(3);
+    return;
+  }
   if (MODE == M_SELECT_K) {
     stream_top_k<VEC, PEN>(P, rc, c, h, row, seen_row, from, end, t);
     PHASE_MARK(3);
@@ -843,6 +881,7 @@ struct SmemMap {
   Shared* sm;
   Ctx* ctx;
   RowCfg* rc;
+  unsigned long long* bars;
   unsigned char* region;  // streaming: bitmap + hash table; finishing: float scratch
 };
 
@@ -853,15 +892,19 @@ __device__ __forceinline__ SmemMap smem_map(unsigned char* raw, int cap, int kee
   m.hist = reinterpret_cast<unsigned*>(m.stage + keep);
   unsigned char* at = reinterpret_cast<unsigned char*>(m.hist + BINS + 32);
   m.sm = reinterpret_cast<Shared*>(at);
-  m.ctx = reinterpret_cast<Ctx*>(at + 128);
-  m.rc = reinterpret_cast<RowCfg*>(at + 256);
+  m.ctx = reinterpret_cast<Ctx*>(at + 256);
+  m.rc = reinterpret_cast<RowCfg*>(at + 384);
+  m.bars = reinterpret_cast<unsigned long long*>(at + 512);
   m.region = at + SMEM_FIXED;
   return m;
 }
-static_assert(sizeof(Shared) <= 128 && sizeof(Ctx) <= 128 && sizeof(RowCfg) <= 128, "slots of 128 bytes");
+static_assert(sizeof(Shared) <= 256 && sizeof(Ctx) <= 128 && sizeof(RowCfg) <= 128, "fixed shared-memory slots");
 
+#ifndef LEAT_MIN_BLOCKS
+#define LEAT_MIN_BLOCKS 2
+#endif
 template <int VEC, bool PEN>
-__global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
+__global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const KParams P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const SmemMap M = smem_map(smem_raw, P.cap, P.keep);
   unsigned long long* buf = M.buf;
@@ -872,6 +915,11 @@ __global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
   float* fw = reinterpret_cast<float*>(M.region);
   float* fi = fw + P.cap;
   float* fs = fi + P.cap;
+  // the ring shares its bytes with the hash table, which is dead once the history pass is over
+  Ring ring;
+  ring.data = reinterpret_cast<float*>(M.region + (((size_t)P.bm_words * 4 + 127) / 128) * 128);
+  ring.bars = M.bars;
+  ring.stages = P.ring_stages;
 
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
   const int b = blockIdx.y, slice = blockIdx.x, S = P.slices;
@@ -889,6 +937,7 @@ __global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
     c.cap = P.cap; c.keep = P.keep; c.mode = rc.mode; c.k = rc.k_eff; c.logm = rc.logm;
     c.divide = rc.divide; c.off = P.vocab_offset; c.begin = begin; c.rinv = rc.rinv; c.tf = rc.tf;
     c.bitmap = (PEN && P.history) ? bitmap : nullptr;
+    c.region = (P.cap - P.keep) / (nt >> 5);
   }
   __syncthreads();
   const int mode = rc.mode;
@@ -928,10 +977,10 @@ __global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
   Tracked t;
   t.gl = neg_inf(); t.gid = NO_ID; t.al = neg_inf(); t.aid = NO_ID;
   t.mnl = __uint_as_float(0x7F800000u); t.mns = t.mnl;
-  if (mode == M_ARGMAX_L) stream_slice<VEC, PEN, M_ARGMAX_L>(P, rc, c, h, row, seen_row, begin, end, t);
-  else if (mode == M_ARGMAX_G) stream_slice<VEC, PEN, M_ARGMAX_G>(P, rc, c, h, row, seen_row, begin, end, t);
-  else if (mode == M_SELECT_K) stream_slice<VEC, PEN, M_SELECT_K>(P, rc, c, h, row, seen_row, begin, end, t);
-  else if (mode == M_SELECT_MINP) stream_slice<VEC, PEN, M_SELECT_MINP>(P, rc, c, h, row, seen_row, begin, end, t);
+  if (mode == M_ARGMAX_L) stream_slice<VEC, PEN, M_ARGMAX_L>(P, rc, c, h, row, seen_row, begin, end, t, ring);
+  else if (mode == M_ARGMAX_G) stream_slice<VEC, PEN, M_ARGMAX_G>(P, rc, c, h, row, seen_row, begin, end, t, ring);
+  else if (mode == M_SELECT_K) stream_slice<VEC, PEN, M_SELECT_K>(P, rc, c, h, row, seen_row, begin, end, t, ring);
+  else if (mode == M_SELECT_MINP) stream_slice<VEC, PEN, M_SELECT_MINP>(P, rc, c, h, row, seen_row, begin, end, t, ring);
   __syncthreads();
 
 #ifdef LEAT_PHASE_CLOCKS
@@ -958,7 +1007,7 @@ __global__ void __launch_bounds__(512, 2) sample_kernel(const KParams P) {
   __syncthreads();
   if ((mode == M_SELECT_K || mode == M_SELECT_MINP) && !sm.overflow) {
     // the stream of a top-k row leaves raw entries behind: the rebuild also turns them into keys
-    if (mode == M_SELECT_MINP || sm.n > rc.k_eff || sm.conv < sm.n) buffer_rebuild(c, mode == M_SELECT_K);
+    buffer_rebuild(c, mode == M_SELECT_K);
   }
   bool failed = (mode == M_GENERAL) || sm.overflow;
 
@@ -1078,7 +1127,7 @@ __global__ void __launch_bounds__(512) finish_candidates_kernel(const KParams P)
   Ctx c;
   c.buf = buf; c.stage = M.stage; c.hist = M.hist; c.sm = M.sm;
   c.cap = P.cap; c.keep = P.keep; c.mode = mode; c.k = rc.k_eff; c.logm = rc.logm;
-  c.divide = 0; c.off = 0; c.begin = 0; c.rinv = 1.0f; c.tf = 1.0f; c.bitmap = nullptr;
+  c.divide = 0; c.off = 0; c.begin = 0; c.rinv = 1.0f; c.tf = 1.0f; c.bitmap = nullptr; c.region = 1;
   if (tid == 0) {
     sm.n = 0; sm.m = 0; sm.conv = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.best = 0ull; sm.gbest = 0ull;
     sm.smin = 0u;

@@ -97,6 +97,9 @@ class Sampler:
     def tune(self, threads: int = 0, slices: int = 0) -> None:
         _lib.check(_lib.lib.leat_sampler_tune(self.handle, threads, slices), "leat_sampler_tune")
 
+    def tune_ring(self, stages: int = 0) -> None:
+        _lib.check(_lib.lib.leat_sampler_tune_ring(self.handle, stages), "leat_sampler_tune_ring")
+
     def plan(self, rows: int, vocab: int, history_cap: int = 0) -> tuple[int, int, int]:
         t, s, b = C.c_int32(), C.c_int32(), C.c_int32()
         _lib.check(_lib.lib.leat_sampler_plan(self.handle, rows, vocab, history_cap, C.byref(t),
