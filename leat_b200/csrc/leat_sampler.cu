@@ -15,7 +15,7 @@ using namespace leat;
 
 namespace {
 
-constexpr int kMaxSliceLen = 131072;  // bitmap of a slice: 16 KB
+constexpr int kMaxSliceLen = 1 << 20;  // a block may take a whole row
 constexpr int kSliceAlign = 128;
 constexpr int kMaxK = 1024;
 constexpr int kSpareCells = 4096;
@@ -78,24 +78,29 @@ size_t fixed_shared(int cap, int keep) {
 }
 
 size_t shared_bytes(int cap, int keep, int bm_words, int ht_size, size_t ring = 0) {
-  size_t bitmap = ((size_t)bm_words * 4 + 127) / 128 * 128;
-  size_t table = (size_t)ht_size * 8;
-  size_t stream = bitmap + (table > ring ? table : ring);
+  (void)bm_words;
+  // the hash keys, then one area shared by their counts, the ring and the scratch of the finish
+  size_t keys = ((size_t)ht_size * 4 + 127) / 128 * 128;
+  size_t counts = (size_t)ht_size * 4;
   size_t finish = (size_t)cap * 8 + (size_t)(cap / 32) * 4;
-  return fixed_shared(cap, keep) + (stream > finish ? stream : finish);
+  size_t later = counts > ring ? counts : ring;
+  if (finish > later) later = finish;
+  return fixed_shared(cap, keep) + keys + later;
 }
 
 Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool has_history, int vec) {
   Plan p;
   p.vec = vec;
-  long long elems = (long long)rows * vocab;
-  p.threads = h->tune_threads ? h->tune_threads : (elems <= (4ll << 20) ? 256 : 512);
+  p.threads = h->tune_threads ? h->tune_threads : 512;
   int step = p.threads * vec * UNROLL;
   int min_slices = (vocab + kMaxSliceLen - 1) / kMaxSliceLen;
   int max_slices = (vocab + step - 1) / step;
   if (max_slices < min_slices) max_slices = min_slices;
-  int per_sm = p.threads >= 512 ? 2 : 4;
-  int want = h->tune_slices ? h->tune_slices : (h->sm_count * per_sm * 4 + rows - 1) / rows;
+  // every block pays a fixed price (set-up, first threshold, final select), so rows are cut no
+  // finer than it takes to give each of the two blocks an SM holds something to do
+  int resident = h->sm_count * 2;
+  int want = h->tune_slices ? h->tune_slices : (resident + rows / 2) / rows;
+  if (!h->tune_slices && want > 8) want = 8;
   int by_cells = h->L.cells / (rows > 0 ? rows : 1);
   if (want > by_cells) want = by_cells;
   if (want > max_slices) want = max_slices;
@@ -105,13 +110,13 @@ Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool
   if (p.slice_len < 1) p.slice_len = kSliceAlign;
   p.slices = (vocab + p.slice_len - 1) / p.slice_len;
   if (p.slices < 1) p.slices = 1;
-  p.bm_words = has_history ? p.slice_len / 32 : 0;
+  p.bm_words = 0;
   p.ht_size = has_history ? next_pow2(history_cap * 2 < 64 ? 64 : history_cap * 2) : 0;
   // the ring of bulk copies: as many stages as fit a block's share of shared memory
   p.ring_stages = 0;
   if (vec == 4 && !h->tune_no_ring) {
     const size_t stage = (size_t)p.threads * 16 * 4;
-    const size_t used = fixed_shared(h->cap, h->keep) + ((size_t)p.bm_words * 4 + 127) / 128 * 128;
+    const size_t used = fixed_shared(h->cap, h->keep) + ((size_t)p.ht_size * 4 + 127) / 128 * 128;
     int stages = used < kSharedPerBlockTarget ? (int)((kSharedPerBlockTarget - used) / stage) : 0;
     if (h->tune_stages) stages = h->tune_stages;
     if (stages > MAX_RING_STAGES) stages = MAX_RING_STAGES;
@@ -167,10 +172,10 @@ int pick_vec(const KParams& P) {
   return ok ? 4 : 1;
 }
 
-template <int VEC, bool PEN>
+template <bool PEN>
 int launch_one(const KParams& P, const Plan& plan, cudaStream_t stream) {
   dim3 grid(plan.slices, P.rows);
-  sample_kernel<VEC, PEN><<<grid, plan.threads, plan.shared, stream>>>(P);
+  sample_kernel<PEN><<<grid, plan.threads, plan.shared, stream>>>(P);
   return cuda_failed(cudaGetLastError(), "sample_kernel launch") ? LEAT_E_CUDA : LEAT_OK;
 }
 
@@ -185,10 +190,8 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
   const int vec = pick_vec(P);
   Plan plan = make_plan(h, P.rows, P.vocab, P.history_cap, P.history != nullptr, vec);
   P.slices = plan.slices; P.slice_len = plan.slice_len; P.bm_words = plan.bm_words; P.ht_size = plan.ht_size;
-  P.ring_stages = (P.seen == nullptr) ? plan.ring_stages : 0;
-  int rc;
-  if (vec == 4) rc = pen ? launch_one<4, true>(P, plan, stream) : launch_one<4, false>(P, plan, stream);
-  else rc = pen ? launch_one<1, true>(P, plan, stream) : launch_one<1, false>(P, plan, stream);
+  P.ring_stages = plan.ring_stages;  // 0 unless rows are 16-byte aligned multiples of four floats
+  int rc = pen ? launch_one<true>(P, plan, stream) : launch_one<false>(P, plan, stream);
   if (rc == LEAT_OK) h->launches += 1;
   return rc;
 }
@@ -229,8 +232,7 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
   }
   h->sm_count = sms > 0 ? sms : 148;
   const int most = 200 * 1024;
-  if (allow_shared(sample_kernel<4, true>, most) || allow_shared(sample_kernel<4, false>, most) ||
-      allow_shared(sample_kernel<1, true>, most) || allow_shared(sample_kernel<1, false>, most) ||
+  if (allow_shared(sample_kernel<true>, most) || allow_shared(sample_kernel<false>, most) ||
       allow_shared(finish_candidates_kernel, most)) {
     delete h; return LEAT_E_CUDA;
   }
@@ -423,8 +425,7 @@ int static_setup(int device, StaticDevice** out) {
       return LEAT_E_CUDA;
     h.sm_count = sms > 0 ? sms : 148;
     const int most = 200 * 1024;
-    if (allow_shared(sample_kernel<4, true>, most) || allow_shared(sample_kernel<4, false>, most) ||
-        allow_shared(sample_kernel<1, true>, most) || allow_shared(sample_kernel<1, false>, most))
+    if (allow_shared(sample_kernel<true>, most) || allow_shared(sample_kernel<false>, most))
       return LEAT_E_CUDA;
     sd.ready = true;
   }
@@ -457,9 +458,9 @@ int leat_sample_static(const leat_sample_args* a, leat_stream_t stream) {
 #ifdef LEAT_PHASE_CLOCKS
 // development build only: cycles spent per phase, summed over blocks; clear != 0 zeroes them
 int leat_debug_phases(unsigned long long* out, int clear) {
-  if (out && cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 16) != cudaSuccess) return -1;
+  if (out && cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 32) != cudaSuccess) return -1;
   if (clear) {
-    unsigned long long zero[16] = {0};
+    unsigned long long zero[32] = {0};
     if (cudaMemcpyToSymbol(g_phase_cycles, zero, sizeof(zero)) != cudaSuccess) return -1;
   }
   return 0;

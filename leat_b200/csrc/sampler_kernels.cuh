@@ -23,12 +23,18 @@
 namespace leat {
 
 #ifdef LEAT_PHASE_CLOCKS
-__device__ unsigned long long g_phase_cycles[16];
+__device__ unsigned long long g_phase_cycles[32];
+#define RB_MARK(i) do { if (threadIdx.x == 0) { long long now_ = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(now_ - rb_t0_)); rb_t0_ = now_; } } while (0)
+#define RB_BEGIN() long long rb_t0_ = clock64()
+#define RB_ADD1(i) atomicAdd(&g_phase_cycles[i], 1ull)
 #define PHASE_MARK(i) do { __syncthreads(); if (threadIdx.x == 0) { long long now_ = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(now_ - phase_t0_)); phase_t0_ = now_; } } while (0)
 #define PHASE_BEGIN() long long phase_t0_ = clock64()
 #else
 #define PHASE_MARK(i) do { } while (0)
 #define PHASE_BEGIN() do { } while (0)
+#define RB_MARK(i) do { } while (0)
+#define RB_BEGIN() do { } while (0)
+#define RB_ADD1(i) do { } while (0)
 #endif
 
 enum RowMode : int {
@@ -88,13 +94,15 @@ struct Shared {
   float tau;     // running threshold on scores
   int overflow;  // the slice / row cannot be reduced to `keep` candidates
   int sel_bin, sel_above, sel_count;
-  unsigned vmin, vmax;
+  unsigned vmin, vmax, smin2, rmin, rmax;
   int is_last;
   unsigned long long best;   // block max of an argmax key
   unsigned long long gbest;  // block max of the greedy key
   unsigned smin;             // block min of score bits (ord32)
   int jstar, ns, pick;
   int wcount[32];  // raw entries each warp holds in its own region of the buffer
+  // the block's best so far, as order-preserving bits: what a logit must reach to be looked at
+  unsigned share_greedy, share_gumbel, share_min;
 };
 
 // what the candidate buffer needs, by value in registers
@@ -109,8 +117,22 @@ struct Ctx {
   int divide, off, begin;
   int region;  // raw slots per warp, after the first `keep` slots of the buffer
   float rinv, tf;
-  const unsigned* bitmap;  // history tokens of the slice (their raw entries are dropped), or null
+  const int* hkeys;  // hash table of the slice's history tokens (their raw entries are dropped), or null
+  int hmask;
 };
+
+// is token `idx` one of the slice's history tokens?  (open addressing, keys only)
+__device__ __forceinline__ bool in_history(const int* keys, int mask, int idx) {
+  uint32_t slot = lowbias32((uint32_t)idx) & mask;
+#pragma unroll 1
+  for (int probe = 0; probe <= mask; ++probe) {
+    const int k = keys[slot];
+    if (k == idx) return true;
+    if (k == -1) return false;
+    slot = (slot + 1) & mask;
+  }
+  return false;
+}
 
 __device__ __forceinline__ float penalised(float l, int count, const RowCfg& rc) {
   float r = l > 0.0f ? l / rc.rep : l * rc.rep;
@@ -185,49 +207,60 @@ __device__ __forceinline__ bool warp_append(unsigned long long* dst, int* counte
   return false;
 }
 
+// One bucket per score: linear in value between `low_v` and the largest score held when `scale` is
+// positive, else by the score's bits above `lo`.
+__device__ __forceinline__ int bucket_of(uint32_t v, float low_v, float scale, uint32_t lo, int shift) {
+  if (scale > 0.0f) return min(BINS - 1, max(0, (int)((unord32(v) - low_v) * scale)));
+  return (int)((v - lo) >> shift);
+}
+
 // Rebuilds the buffer around a new threshold.  All threads of the block call it together, after a
 // barrier that made every append visible.  M_SELECT_K: the threshold is a score with at least k
-// and at most `keep` entries at or above it, found coarse to fine: 2048 buckets over the range the
-// entries span, then over the bucket that holds the k-th largest, until few enough remain (the
-// k-th largest itself at the finest step).  M_SELECT_MINP: the largest score held plus log(min_p).
-// Every entry at or above the threshold stays; sm.tau becomes the threshold.
+// and little more than k entries at or above it (at most `keep`), found coarse to fine over 2048
+// buckets: by value first, so that scores spread evenly and the counting atomics rarely meet, then
+// by the chosen bucket's bits.  M_SELECT_MINP: the largest score held plus log(min_p).  Every entry
+// at or above the threshold stays; sm.tau becomes the threshold.
+//
+// Raw mode: slots [0, conv) hold keys and warp w's raw (logit, index) pairs sit in
+// [keep + w * region, ... + wcount[w]); every other slot is ignored.  Otherwise slots [0, n) hold
+// keys.  On entry the histogram is zero and vmin / vmax / m / valid are reset (kernel start and the
+// end of every rebuild see to that), which keeps the barriers down to five.
 __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
   Shared& sm = *c.sm;
   unsigned long long* buf = c.buf;
   unsigned* hist = c.hist;
-  unsigned* wtot = c.hist + BINS;
-  const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
-  // raw mode: slots [0, conv) hold keys, [conv, keep) are empty, and warp w's raw (logit, index)
-  // pairs sit in [keep + w * region, ... + wcount[w]); every other slot is taken as empty
+  const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, nwarps = nt >> 5;
+  RB_BEGIN();
   const int region = c.region;
+  const int conv = sm.conv;
   const int n = raw ? c.keep + nwarps * region : min(sm.n, c.cap);
-  if (tid == 0) { sm.vmin = 0xFFFFFFFFu; sm.vmax = 0u; sm.m = 0; sm.valid = 0; }
-  __syncthreads();
+  // ---- A: make raw pairs keys; smallest, largest and number of live keys ----
   {
     const float tau = sm.tau;
     uint32_t mx = 0u, mn = 0xFFFFFFFFu;
     int live = 0;
+#pragma unroll 1
     for (int i = tid; i < n; i += nt) {
-      unsigned long long key = buf[i];
-      if (raw && i >= c.keep) {
-        // make a raw pair a key; a history token's raw logit is dropped (the history pass gave
-        // its penalised one), and so is anything below the threshold it was appended under
+      unsigned long long key = 0ull;
+      if (!raw || i < conv) {
+        key = buf[i];
+      } else if (i >= c.keep) {
+        // a history token's raw logit is dropped (the history pass gave its penalised one), and
+        // so is anything below the threshold it was appended under
         const int w = (i - c.keep) / region;
-        const bool held = (i - c.keep) - w * region < sm.wcount[w];
-        const float l = __uint_as_float((uint32_t)(key >> 32));
-        const int idx = (int)(uint32_t)key;
-        bool drop = !held;
-        if (held && c.bitmap) {
-          const int local = idx - c.begin;
-          drop = (c.bitmap[local >> 5] >> (local & 31)) & 1u;
+        if ((i - c.keep) - w * region < sm.wcount[w]) {
+          const unsigned long long pair = buf[i];
+          const float l = __uint_as_float((uint32_t)(pair >> 32));
+          const int idx = (int)(uint32_t)pair;
+          bool drop = false;
+          if (c.hkeys) drop = in_history(c.hkeys, c.hmask, idx);
+          const float sc = c.divide ? l / c.tf : l * c.rinv;
+          if (!drop && sc >= tau) key = make_key(sc, (uint32_t)(idx + c.off));
         }
-        const float sc = c.divide ? l / c.tf : l * c.rinv;
-        if (!(sc >= tau)) drop = true;
-        key = drop ? 0ull : make_key(sc, (uint32_t)(idx + c.off));
-        buf[i] = key;
       }
+      if (raw) buf[i] = key;
       if (key) {
-        uint32_t v = key_vbits(key);
+        const uint32_t v = key_vbits(key);
         mx = max(mx, v);
         mn = min(mn, v);
         live += 1;
@@ -236,88 +269,154 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
     mx = __reduce_max_sync(FULL, mx);
     mn = __reduce_min_sync(FULL, mn);
     live = __reduce_add_sync(FULL, live);
-    if (lane == 0) { atomicMax(&sm.vmax, mx); atomicMin(&sm.vmin, mn); atomicAdd(&sm.valid, live); }
+    if (lane == 0 && live) { atomicMax(&sm.vmax, mx); atomicMin(&sm.vmin, mn); atomicAdd(&sm.valid, live); }
   }
   __syncthreads();
+  RB_MARK(16);
   const int live = sm.valid;
-  uint32_t thr = 1u;  // every live entry (key bits of any score exceed 0)
-  if (live == 0) {
-    thr = 1u;
-  } else if (c.mode == M_SELECT_MINP) {
-    thr = ord32(unord32(sm.vmax) + c.logm + 0.0f);
+  uint32_t lo = sm.vmin, hi = sm.vmax;  // the k-th largest lies in [lo, hi]
+  uint32_t thr = 1u;                    // keep every live entry (key bits of any score exceed 0)
+  float low_v = 0.0f, scale = 0.0f;     // the bucket function of the accepted step
+  int shift = 0, chosen = 0;
+  bool by_bucket = false;
+  if (live > 0 && c.mode == M_SELECT_MINP) {
+    thr = ord32(unord32(hi) + c.logm + 0.0f);
   } else if (live > c.k) {
-    uint32_t lo = sm.vmin, hi = sm.vmax;  // the k-th largest lies in [lo, hi]
-    unsigned above = 0u;                  // entries above hi
-    unsigned rem = (unsigned)c.k;         // the one sought is the rem-th largest within [lo, hi]
-    const int per = BINS / nt;
-    for (int pass = 0; pass < 4; ++pass) {
-      const uint32_t range = hi - lo;
-      if (range == 0u) { thr = lo; break; }
-      const int bits = 32 - __clz(range);
-      const int shift = bits > 11 ? bits - 11 : 0;
-      for (int i = tid; i < BINS; i += nt) hist[i] = 0u;
-      __syncthreads();
+    unsigned above = 0u;           // entries above hi
+    unsigned rem = (unsigned)c.k;  // the one sought is the rem-th largest within [lo, hi]
+    const float top_v = unord32(hi);
+    low_v = fmaxf(unord32(lo), top_v - 64.0f);
+    scale = (float)(BINS - 1) / (top_v - low_v);
+    if (!(top_v > low_v && scale > 0.0f && scale < 3.0e38f)) scale = 0.0f;
+#pragma unroll 1
+    for (int pass = 0; pass < 5; ++pass) {
+      if (hi == lo) { thr = lo; by_bucket = false; break; }
+      const int bits = 32 - __clz(hi - lo);
+      shift = bits > 11 ? bits - 11 : 0;
+      if (pass > 0) {  // the histogram is dirty and the bucket's own range is wanted: one more barrier
+#pragma unroll 1
+        for (int i = tid; i < BINS; i += nt) hist[i] = 0u;
+        __syncthreads();
+      }
+      // ---- B: count ----
+#pragma unroll 1
       for (int i = tid; i < n; i += nt) {
         const unsigned long long key = buf[i];
-        uint32_t v = key_vbits(key);
-        if (key && v >= lo && v <= hi) atomicAdd(&hist[(v - lo) >> shift], 1u);
+        const uint32_t v = key_vbits(key);
+        if (key && v >= lo && v <= hi) atomicAdd(&hist[bucket_of(v, low_v, scale, lo, shift)], 1u);
       }
       __syncthreads();
-      // thread t owns buckets BINS-1 - t*per - j, j < per: highest first
-      unsigned local = 0u;
-      for (int j = 0; j < per; ++j) local += hist[BINS - 1 - tid * per - j];
-      unsigned incl = local;
+      RB_MARK(18);
+      // ---- C: the block walks the buckets from the top ----
+      {
+        unsigned* wtot = hist + BINS;
+        const int per = BINS / nt;
+        const int warp = tid >> 5;
+        // thread t owns buckets BINS-1 - t*per - j, j < per: highest first
+        unsigned local = 0u;
+#pragma unroll 4
+        for (int j = 0; j < per; ++j) local += hist[BINS - 1 - tid * per - j];
+        unsigned incl = local;
 #pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        unsigned o = __shfl_up_sync(FULL, incl, d);
-        if (lane >= d) incl += o;
-      }
-      if (lane == 31) wtot[warp] = incl;
-      __syncthreads();
-      unsigned before = 0u;
-      for (int w = 0; w < warp; ++w) before += wtot[w];
-      unsigned acc = before + incl - local;  // entries in buckets above this thread's
-      if (acc < rem && rem <= acc + local) {
-        for (int j = 0; j < per; ++j) {
-          unsigned cnt = hist[BINS - 1 - tid * per - j];
-          if (acc < rem && rem <= acc + cnt) {
-            sm.sel_bin = BINS - 1 - tid * per - j;
-            sm.sel_above = (int)acc;
-            sm.sel_count = (int)cnt;
+        for (int d = 1; d < 32; d <<= 1) {
+          unsigned o = __shfl_up_sync(FULL, incl, d);
+          if (lane >= d) incl += o;
+        }
+        if (lane == 31) wtot[warp] = incl;
+        __syncthreads();
+        unsigned before = 0u;
+#pragma unroll 1
+        for (int w = 0; w < warp; ++w) before += wtot[w];
+        unsigned acc = before + incl - local;  // entries in buckets above this thread's
+        if (acc < rem && rem <= acc + local) {
+#pragma unroll 1
+          for (int j = 0; j < per; ++j) {
+            const unsigned cnt = hist[BINS - 1 - tid * per - j];
+            if (acc < rem && rem <= acc + cnt) {
+              sm.sel_bin = BINS - 1 - tid * per - j;
+              sm.sel_above = (int)acc;
+              sm.sel_count = (int)cnt;
+            }
+            acc += cnt;
           }
-          acc += cnt;
         }
       }
       __syncthreads();
-      const uint32_t edge = lo + ((uint32_t)sm.sel_bin << shift);
+      RB_MARK(19);
+      chosen = sm.sel_bin;
       const unsigned at_or_above = above + (unsigned)sm.sel_above + (unsigned)sm.sel_count;
+      const bool finest = scale == 0.0f && shift == 0;
       // accept a threshold that keeps little more than k: a loose one lets too much through later
-      if (at_or_above <= (unsigned)min(c.keep, c.k + max(8, c.k >> 3)) || shift == 0) { thr = edge; break; }
+      if (at_or_above <= (unsigned)min(c.keep, c.k + max(8, c.k >> 3)) || finest) {
+        by_bucket = true;
+        break;
+      }
+      // refine inside the chosen bucket: its own smallest and largest score bits
+      {
+        uint32_t mx = 0u, mn = 0xFFFFFFFFu;
+#pragma unroll 1
+        for (int i = tid; i < n; i += nt) {
+          const unsigned long long key = buf[i];
+          const uint32_t v = key_vbits(key);
+          if (key && v >= lo && v <= hi && bucket_of(v, low_v, scale, lo, shift) == chosen) {
+            mx = max(mx, v);
+            mn = min(mn, v);
+          }
+        }
+        mx = __reduce_max_sync(FULL, mx);
+        mn = __reduce_min_sync(FULL, mn);
+        if (lane == 0 && mx >= mn) { atomicMax(&sm.rmax, mx); atomicMin(&sm.rmin, mn); }
+      }
+      __syncthreads();
       above += (unsigned)sm.sel_above;
       rem -= (unsigned)sm.sel_above;
-      const uint32_t last = edge + ((1u << shift) - 1u);
-      lo = edge;
-      hi = last < hi ? last : hi;
-      (void)nwarps;
+      lo = sm.rmin;
+      hi = sm.rmax;
+      scale = 0.0f;
+      __syncthreads();  // everyone has read the range before it is reset for the next step
+      if (tid == 0) { sm.rmin = 0xFFFFFFFFu; sm.rmax = 0u; }
     }
   }
-  // survivors go to the staging area, then back to the front of the buffer
-  for (int base = 0; base < n; base += nt) {
-    int i = base + tid;
-    unsigned long long key = (i < n) ? buf[i] : 0ull;
-    warp_append(c.stage, &sm.m, c.keep, key != 0ull && key_vbits(key) >= thr, key);
+  RB_MARK(21);
+  if (threadIdx.x == 0) { RB_ADD1(24); }
+  // ---- D: survivors go to the staging area; the smallest of them is the new threshold ----
+  {
+    uint32_t mn = 0xFFFFFFFFu;
+#pragma unroll 1
+    for (int base = 0; base < n; base += nt) {
+      const int i = base + tid;
+      const unsigned long long key = (i < n) ? buf[i] : 0ull;
+      const uint32_t v = key_vbits(key);
+      bool stay = key != 0ull;
+      if (stay && by_bucket) stay = v > hi || (v >= lo && bucket_of(v, low_v, scale, lo, shift) >= chosen);
+      else if (stay) stay = v >= thr;
+      if (stay) mn = min(mn, v);
+      warp_append(c.stage, &sm.m, c.keep, stay, key);
+    }
+    mn = __reduce_min_sync(FULL, mn);
+    if (by_bucket && lane == 0) atomicMin(&sm.smin2, mn);
   }
   __syncthreads();
+  RB_MARK(22);
+  // ---- E: back to the front of the buffer ----
   const int m = min(sm.m, c.keep);
-  for (int i = tid; i < c.keep; i += nt) buf[i] = (i < m) ? c.stage[i] : 0ull;
+  if (by_bucket) thr = sm.smin2;
+#pragma unroll 1
+  for (int i = tid; i < m; i += nt) buf[i] = c.stage[i];
+#pragma unroll 1
+  for (int i = tid; i < BINS; i += nt) hist[i] = 0u;
   if (tid < 32) sm.wcount[tid] = 0;
+  const bool over = sm.m > c.keep;
+  __syncthreads();
   if (tid == 0) {
-    if (sm.m > c.keep) sm.overflow = 1;
+    if (over) sm.overflow = 1;
     sm.n = m;
     sm.conv = m;
-    if (thr > 1u) sm.tau = fmaxf(sm.tau, unord32(thr));
+    if (thr > 1u && thr != 0xFFFFFFFFu) sm.tau = fmaxf(sm.tau, unord32(thr));
+    sm.vmin = 0xFFFFFFFFu; sm.vmax = 0u; sm.m = 0; sm.valid = 0; sm.smin2 = 0xFFFFFFFFu;
   }
   __syncthreads();
+  RB_MARK(23);
 }
 
 // Block-synchronous append of one optional entry per thread (the merge of a row's slices).
@@ -337,8 +436,11 @@ __device__ inline void buffer_push(const Ctx& c, bool want, unsigned long long k
 // descending bitonic sort of buf[0..p2), p2 a power of two
 __device__ inline void block_sort_desc(unsigned long long* buf, int p2) {
   const int tid = threadIdx.x, nt = blockDim.x;
+#pragma unroll 1
   for (int k = 2; k <= p2; k <<= 1) {
+#pragma unroll 1
     for (int j = k >> 1; j > 0; j >>= 1) {
+#pragma unroll 1
       for (int i = tid; i < p2; i += nt) {
         int x = i ^ j;
         if (x > i) {
@@ -358,6 +460,7 @@ __device__ inline void block_sort_desc(unsigned long long* buf, int p2) {
 // single pass could not reduce.
 __device__ inline void finish_simple(const KParams& P, int b, int mode, unsigned long long best,
                                      unsigned long long gbest, bool failed) {
+#pragma unroll 1
   for (int j = threadIdx.x; j < P.out_width; j += blockDim.x) {
     if (P.out_probs) P.out_probs[(size_t)b * P.out_width + j] = 0.0f;
     if (P.out_prob_ids) P.out_prob_ids[(size_t)b * P.out_width + j] = -1;
@@ -386,15 +489,37 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
     finish_simple(P, b, rc.mode, 0ull, 0ull, true);
     return;
   }
-  int p2 = 1;
-  while (p2 < n) p2 <<= 1;
-  for (int i = n + tid; i < p2; i += nt) buf[i] = 0ull;
   if (tid == 0) { sm.jstar = 0; sm.ns = 0; sm.pick = NO_ID; sm.best = 0ull; }
-  __syncthreads();
-  block_sort_desc(buf, p2);
+  if (n <= P.cap / 2) {
+    // few candidates: a key's place is the number of keys above it (keys are distinct), one
+    // sweep over shared memory and no barriers, into the buffer's upper half
+    unsigned long long* sorted = buf + P.cap / 2;
+#pragma unroll 1
+    for (int i = tid; i < n; i += nt) {
+      const unsigned long long key = buf[i];
+      int rank = 0;
+      int j = 0;
+#pragma unroll 1
+      for (; j + 4 <= n; j += 4)
+        rank += (buf[j] > key) + (buf[j + 1] > key) + (buf[j + 2] > key) + (buf[j + 3] > key);
+#pragma unroll 1
+      for (; j < n; ++j) rank += buf[j] > key;
+      sorted[rank] = key;
+    }
+    __syncthreads();
+    buf = sorted;
+  } else {
+    int p2 = 1;
+    while (p2 < n) p2 <<= 1;
+#pragma unroll 1
+    for (int i = n + tid; i < p2; i += nt) buf[i] = 0ull;
+    __syncthreads();
+    block_sort_desc(buf, p2);
+  }
   const float top = key_value(buf[0]);
   const int in_k = min(rc.k_eff, n);
   const int nseg = (n + 31) >> 5;
+#pragma unroll 1
   for (int s = warp; s < nseg; s += nwarps) {
     int j = s * 32 + lane;
     float w = 0.0f;
@@ -411,13 +536,16 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
   __syncthreads();
   if (tid == 0) {
     float off = 0.0f;
+#pragma unroll 1
     for (int s = 0; s < nseg; ++s) { float t = fs[s]; fs[s] = off; off = off + t; }
   }
   __syncthreads();
+#pragma unroll 1
   for (int j = tid; j < n; j += nt) fi[j] = fs[j >> 5] + fi[j];
   __syncthreads();
   const float kept = fi[in_k - 1];
   const float bound_p = rc.p * kept;
+#pragma unroll 1
   for (int j = tid; j < in_k; j += nt) {
     float likelier = fi[j] - fw[j];
     if (j == 0 || likelier < bound_p) atomicMax(&sm.jstar, j);
@@ -427,6 +555,7 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
   if (rc.mode == M_SELECT_MINP) base = row_min;  // k = 0: the k-th score is the row's last
   float cut = fmaxf(base, top + rc.logm);
   if (!rc.has_cut) cut = neg_inf();
+#pragma unroll 1
   for (int j = tid; j < n; j += nt) {
     float r = key_value(buf[j]);
     if (r >= cut && (j + 1 == n || !(key_value(buf[j + 1]) >= cut))) sm.ns = j + 1;
@@ -436,10 +565,12 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
   const float total = fi[ns - 1];
   if (P.uniform) {
     const float bound_u = rc.u * total;
+#pragma unroll 1
     for (int j = tid; j < ns; j += nt)
       if (fi[j] > bound_u) atomicMin(&sm.pick, j);
   } else {
     unsigned long long best = 0ull;
+#pragma unroll 1
     for (int j = tid; j < ns; j += nt) {
       uint32_t id = (uint32_t)key_id(buf[j]);
       float d = key_value(buf[j]) + gumbel(hashed_uniform(id, rc.rkey));
@@ -460,6 +591,7 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
     if (P.status && P.out_probs && sm.ns > P.out_width) atomicOr(P.status, 2);
   }
   if (P.out_probs || P.out_prob_ids) {
+#pragma unroll 1
     for (int j = tid; j < P.out_width; j += nt) {
       if (P.out_probs) P.out_probs[(size_t)b * P.out_width + j] = (j < ns) ? fw[j] / total : 0.0f;
       if (P.out_prob_ids) P.out_prob_ids[(size_t)b * P.out_width + j] = (j < ns) ? key_id(buf[j]) : -1;
@@ -470,7 +602,6 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
 // ---- streaming a slice --------------------------------------------------------------------------
 
 struct History {
-  const unsigned* bitmap;
   const int* keys;
   const int* counts;
   int mask;
@@ -478,9 +609,8 @@ struct History {
 };
 
 __device__ __forceinline__ int history_count(const History& h, int idx) {
-  int local = idx - h.begin;
-  if (!((h.bitmap[local >> 5] >> (local & 31)) & 1u)) return 0;
   uint32_t slot = lowbias32((uint32_t)idx) & h.mask;
+#pragma unroll 1
   for (int probe = 0; probe <= h.mask; ++probe) {
     int k = h.keys[slot];
     if (k == idx) return h.counts[slot];
@@ -492,8 +622,8 @@ __device__ __forceinline__ int history_count(const History& h, int idx) {
 
 // the penalised logit of element idx, whose raw logit is l
 template <bool PEN>
-__device__ __forceinline__ float exact_logit(const KParams& P, const RowCfg& rc, const History& h,
-                                             const uint8_t* seen_row, int idx, float l) {
+__device__ __noinline__ float exact_logit(const KParams& P, const RowCfg& rc, const History& h,
+                                          const uint8_t* seen_row, int idx, float l) {
   if (PEN) {
     int count = P.history ? history_count(h, idx) : 0;
     if (seen_row && seen_row[idx]) count = max(count, 1);
@@ -502,160 +632,188 @@ __device__ __forceinline__ float exact_logit(const KParams& P, const RowCfg& rc,
   return l;
 }
 
-template <int N>
-__device__ __forceinline__ float pick(const float (&v)[N], int q) {
-  float r = v[0];
-#pragma unroll
-  for (int i = 1; i < N; ++i) r = (q == i) ? v[i] : r;
-  return r;
-}
-
-template <int VEC>
-struct Chunk {
-  float v[UNROLL * VEC];
-  uint32_t seen[UNROLL];  // VEC seen bytes per vector, packed
+struct Tracked {
+  float gl; int gid;  // best penalised logit and where (greedy)
+  float al; int aid;  // best score + gumbel and where
+  float mnl;          // smallest unpenalised logit
+  float mns;          // smallest score among penalised elements
 };
 
-template <int VEC, bool PEN>
-__device__ __forceinline__ void load_chunk(Chunk<VEC>& c, const float* __restrict__ row,
-                                           const uint8_t* __restrict__ seen_row, int first, int stride,
-                                           int end) {
+#include "stream_ring.cuh"
+
+// The first `cap` scores of a top-k / min-p slice go straight into the candidate buffer (exact,
+// penalties applied); one rebuild gives the first threshold.  Returns where the stream starts.
+template <bool PEN>
+__device__ __noinline__ int slice_fill(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
+                                       const float* __restrict__ row, const uint8_t* __restrict__ seen_row,
+                                       int begin, int end, Tracked& t) {
+  Shared& sm = *c.sm;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int fill_end = min(end, begin + c.cap);
+  constexpr int FB = 4;  // loads in flight per thread
+#pragma unroll 1
+  for (int base = begin; base < fill_end; base += nt * FB) {
+    float raw[FB];
 #pragma unroll
-  for (int u = 0; u < UNROLL; ++u) {
-    int idx = first + u * stride;
-    bool in = idx < end;
-    if (VEC == 4) {
-      float4 t = make_float4(quiet_nan(), quiet_nan(), quiet_nan(), quiet_nan());
-      if (in) t = __ldcs(reinterpret_cast<const float4*>(row + idx));
-      c.v[u * VEC + 0] = t.x; c.v[u * VEC + 1] = t.y; c.v[u * VEC + 2] = t.z; c.v[u * VEC + 3] = t.w;
-      if (PEN) c.seen[u] = (in && seen_row) ? __ldcs(reinterpret_cast<const unsigned*>(seen_row + idx)) : 0u;
-    } else {
-      c.v[u] = in ? __ldcs(row + idx) : quiet_nan();
-      if (PEN) c.seen[u] = (in && seen_row) ? (unsigned)__ldcs(seen_row + idx) : 0u;
+    for (int j = 0; j < FB; ++j) {
+      const int i = base + j * nt + tid;
+      raw[j] = i < fill_end ? row[i] : 0.0f;
+    }
+#pragma unroll 1
+    for (int j = 0; j < FB; ++j) {
+      const int i = base + j * nt + tid;
+      if (i < fill_end) {
+        float l = exact_logit<PEN>(P, rc, h, seen_row, i, j == 0 ? raw[0] : j == 1 ? raw[1] : j == 2 ? raw[2] : raw[3]);
+        if (rc.track && (l > t.gl || (l == t.gl && i < t.gid))) { t.gl = l; t.gid = i; }
+        float s = scaled(l, rc);
+        if (!(s == s)) s = neg_inf();
+        if (rc.mode == M_SELECT_MINP) t.mns = fminf(t.mns, s);
+        c.buf[i - begin] = make_key(s, (uint32_t)(i + P.vocab_offset));
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) sm.n = fill_end - begin;
+  __syncthreads();
+  if (end > fill_end) buffer_rebuild(c, 0);
+  return fill_end;
+}
+
+// The penalised tokens of a slice come from the history table, not from the stream: one scattered
+// load each (issued in batches), so the stream never has to penalise a logit.
+template <bool PEN>
+__device__ __noinline__ void slice_history(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
+                                           const float* __restrict__ row, const uint8_t* __restrict__ seen_row,
+                                           int from, int end, Tracked& t) {
+  Shared& sm = *c.sm;
+  const int nt = blockDim.x, tid = threadIdx.x;
+  const int mode = rc.mode;
+  const bool select = mode == M_SELECT_K || mode == M_SELECT_MINP;
+  constexpr int HB = 8;  // table slots per thread per batch
+#pragma unroll 1
+  for (int base = 0; base < h.mask + 1; base += nt * HB) {
+    int idxs[HB], counts[HB];
+    float raw[HB];
+#pragma unroll
+    for (int j = 0; j < HB; ++j) {
+      const int slot = base + j * nt + tid;
+      int idx = (slot <= h.mask) ? h.keys[slot] : HASH_EMPTY;
+      if (idx != HASH_EMPTY && !(idx >= from && idx < end)) idx = HASH_EMPTY;
+      idxs[j] = idx;
+      counts[j] = idx != HASH_EMPTY ? h.counts[slot] : 0;
+      raw[j] = idx != HASH_EMPTY ? row[idx] : 0.0f;
+    }
+    unsigned long long keys[HB];
+    unsigned pending = 0u;
+#pragma unroll 1
+    for (int j = 0; j < HB; ++j) {
+      const int idx = idxs[j];
+      keys[j] = 0ull;
+      if (idx != HASH_EMPTY) {
+        int count = counts[j];
+        if (seen_row && seen_row[idx]) count = max(count, 1);
+        float l = penalised(raw[j], count, rc);
+        if (rc.track && (l > t.gl || (l == t.gl && idx < t.gid))) { t.gl = l; t.gid = idx; }
+        float s = scaled(l, rc);
+        if (mode == M_SELECT_MINP) t.mns = fminf(t.mns, s);
+        if (mode == M_ARGMAX_G) {
+          float d = s + gumbel(hashed_uniform((uint32_t)(idx + P.vocab_offset), rc.rkey));
+          if (d > t.al || (d == t.al && idx < t.aid)) { t.al = d; t.aid = idx; }
+        }
+        if (select && s >= sm.tau) {
+          keys[j] = make_key(s, (uint32_t)(idx + P.vocab_offset));
+          pending |= 1u << j;
+        }
+      }
+    }
+    if (select) {
+      // one barrier per batch unless the buffer runs out
+      int rounds = 0;
+      while (true) {
+#pragma unroll 1
+        for (int j = 0; j < HB; ++j) {
+          const bool fit = warp_append(c.buf, &sm.n, c.cap, (pending >> j) & 1u, keys[j]);
+          if (fit) pending &= ~(1u << j);
+        }
+        if (!__syncthreads_or(pending != 0u)) break;
+        buffer_rebuild(c, 0);
+        if (sm.overflow || ++rounds > 64) break;
+#pragma unroll 1
+        for (int j = 0; j < HB; ++j)
+          if (((pending >> j) & 1u) && !(key_value(keys[j]) >= sm.tau)) pending &= ~(1u << j);
+      }
+      if (sm.overflow) break;
     }
   }
 }
 
-struct Tracked {
-  float gl; int gid;  // best penalised logit and where (greedy)
-  float al; int aid;  // best score + gumbel and where
-  float mnl;          // smallest raw unpenalised logit
-  float mns;          // smallest score among penalised elements
-};
-
-// The hot loop of top-k rows: [from, end) of one row against a running threshold.  A thread
-// compares its sixteen raw logits with a floor under which no logit can reach the threshold score;
-// the few at or above it are appended as raw (logit, index) pairs, which the next rebuild turns
-// into (score, id) keys (dropping history tokens, whose penalised logits came from the history
-// pass).  One barrier per step tells the block whether an append ran out of buffer.
-template <int VEC, bool PEN>
-__device__ __noinline__ void stream_top_k(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
+// The stream for rows the ring cannot take (a vocabulary or a stride that is not a multiple of four
+// floats): scalar loads, eight logits per thread per step, every logit looked at exactly.  Compact
+// rather than fast.
+template <bool PEN>
+__device__ __noinline__ void stream_plain(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
                                           const float* __restrict__ row, const uint8_t* __restrict__ seen_row,
                                           int from, int end, Tracked& t) {
   Shared& sm = *c.sm;
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
-  constexpr int N = UNROLL * VEC;
-  // keys so far fit the first `keep` slots; the rest of the buffer is one raw region per warp
-  if (sm.n > c.keep) buffer_rebuild(c, 0);
-  for (int i = sm.n + tid; i < c.keep; i += nt) c.buf[i] = 0ull;
-  if (tid < 32) sm.wcount[tid] = 0;
-  if (tid == 0) sm.conv = sm.n;
+  const int mode = rc.mode;
+  const bool select = mode == M_SELECT_K || mode == M_SELECT_MINP;
+  constexpr int PER = 8;
+  if (select) {
+    if (sm.n > c.keep) buffer_rebuild(c, 0);
+#pragma unroll 1
+    for (int i = sm.n + tid; i < c.keep; i += nt) c.buf[i] = 0ull;
+    if (tid < 32) sm.wcount[tid] = 0;
+    if (tid == 0) sm.conv = sm.n;
+  }
   __syncthreads();
   const int region = c.region;
   unsigned long long* const mine = c.buf + c.keep + warp * region;
-  int held = 0;  // raw entries in this warp's region (the same in every lane)
-  float floor_l = logit_floor(sm.tau, rc.tf);
-  bool stop = sm.overflow != 0;
-  const int stride = nt * VEC;
-  const int span = stride * UNROLL;
-  Chunk<VEC> cur, nxt;
-  if (!stop) load_chunk<VEC, PEN>(cur, row, seen_row, from + tid * VEC, stride, end);
-  for (int base = from; base < end && !stop; base += span) {
-    const int first = base + tid * VEC;
-    if (base + span < end) load_chunk<VEC, PEN>(nxt, row, seen_row, first + span, stride, end);
-    unsigned pm = 0u;  // logits at or above the floor
-    unsigned xm = 0u;  // elements under a dense seen mask: penalised one by one
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      if (PEN && cur.seen[u]) {
-        xm |= ((1u << VEC) - 1u) << (u * VEC);
-      } else {
-#pragma unroll
-        for (int e = 0; e < VEC; ++e)
-          if (cur.v[u * VEC + e] >= floor_l) pm |= 1u << (u * VEC + e);
-      }
-    }
-    if (rc.track) {
-      float m = neg_inf();
-#pragma unroll
-      for (int q = 0; q < N; ++q)
-        if (!((xm >> q) & 1u)) m = fmaxf(m, cur.v[q]);
-      if (m > t.gl) {
-#pragma unroll
-        for (int q = 0; q < N; ++q) {
-          const int idx = first + (q / VEC) * stride + (q % VEC);
-          const float l = cur.v[q];
-          if (l > t.gl && !((xm >> q) & 1u)) {
-            bool penalised_elsewhere = false;
-            if (PEN && P.history) {
-              const int local = idx - h.begin;
-              penalised_elsewhere = (h.bitmap[local >> 5] >> (local & 31)) & 1u;
-            }
-            if (!penalised_elsewhere) { t.gl = l; t.gid = idx; }
-          }
-        }
-      }
-    }
+  int held = 0;
+  float floor_l = select ? logit_floor(sm.tau, rc.tf) : 0.0f;
+  bool stop = select && sm.overflow != 0;
+#pragma unroll 1
+  for (int base = from; base < end && !stop; base += nt * PER) {
+    unsigned todo = (1u << PER) - 1u;  // elements of this step still to be placed
     int rounds = 0;
     while (true) {
-      unsigned redo = 0u, xredo = 0u;
-      if (PEN) {
-        while (__any_sync(FULL, xm != 0u)) {
-          const bool have = xm != 0u;
-          const int q = have ? __ffs(xm) - 1 : 0;
-          xm &= xm - 1u;
-          const int idx = first + (q / VEC) * stride + (q % VEC);
-          bool want = false;
-          float l = 0.0f;
-          if (have && idx < end) {
-            l = exact_logit<PEN>(P, rc, h, seen_row, idx, pick(cur.v, q));
-            if (rc.track && (l > t.gl || (l == t.gl && idx < t.gid))) { t.gl = l; t.gid = idx; }
-            want = l >= floor_l;
+      unsigned redo = 0u;
+#pragma unroll 1
+      for (int j = 0; j < PER; ++j) {
+        const int idx = base + j * nt + tid;
+        bool want = false;
+        float l = 0.0f;
+        if (((todo >> j) & 1u) && idx < end) {
+          bool in_history = false;
+          if (PEN && P.history) in_history = leat::in_history(h.keys, h.mask, idx);
+          if (!in_history) {
+            l = row[idx];
+            if (PEN && seen_row && seen_row[idx]) l = penalised(l, 1, rc);
+            if (rounds == 0) {
+              if ((mode == M_ARGMAX_L || rc.track) && (l > t.gl || (l == t.gl && idx < t.gid))) { t.gl = l; t.gid = idx; }
+              const float sc = scaled(l, rc);
+              if (mode == M_SELECT_MINP) t.mns = fminf(t.mns, sc);
+              if (mode == M_ARGMAX_G && sc + GUMBEL_MAX >= t.al) {
+                const float d = sc + gumbel(hashed_uniform((uint32_t)(idx + P.vocab_offset), rc.rkey));
+                if (d > t.al || (d == t.al && idx < t.aid)) { t.al = d; t.aid = idx; }
+              }
+            }
+            want = select && l >= floor_l;
           }
+        }
+        if (select) {
           const unsigned mask = __ballot_sync(FULL, want);
           if (want) {
             const int slot = held + __popc(mask & ((1u << lane) - 1u));
             if (slot < region) mine[slot] = ((unsigned long long)__float_as_uint(l) << 32) | (uint32_t)idx;
-            else xredo |= 1u << q;
+            else redo |= 1u << j;
           }
           held = min(held + __popc(mask), region);
         }
       }
-      if (__any_sync(FULL, pm != 0u)) {
-        // the warp's passing logits go to its own region: no atomics, one scan over the lanes
-        const int count = __popc(pm);
-        int incl = count;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-          const int o = __shfl_up_sync(FULL, incl, d);
-          if (lane >= d) incl += o;
-        }
-        const int total = __shfl_sync(FULL, incl, 31);
-        int slot = held + incl - count;
-#pragma unroll
-        for (int q = 0; q < N; ++q) {
-          if ((pm >> q) & 1u) {
-            const int idx = first + (q / VEC) * stride + (q % VEC);
-            if (slot < region) mine[slot] = ((unsigned long long)__float_as_uint(cur.v[q]) << 32) | (uint32_t)idx;
-            else redo |= 1u << q;
-            ++slot;
-          }
-        }
-        held = min(held + total, region);
-      }
+      if (!select) break;
       if (lane == 0) sm.wcount[warp] = held;
-      // one barrier per step: did any warp run out of room?
-      if (!__syncthreads_or((redo | xredo) != 0u)) break;
+      if (!__syncthreads_or(redo != 0u)) break;
       buffer_rebuild(c, 1);
       held = 0;
       floor_l = logit_floor(sm.tau, rc.tf);
@@ -664,212 +822,9 @@ __device__ __noinline__ void stream_top_k(const KParams& P, const RowCfg& rc, co
         stop = true;
         break;
       }
-      pm = 0u;
-#pragma unroll
-      for (int q = 0; q < N; ++q)
-        if (((redo >> q) & 1u) && cur.v[q] >= floor_l) pm |= 1u << q;
-      xm = xredo;
-    }
-    cur = nxt;
-  }
-}
-
-#include "stream_ring.cuh"
-
-// Streams [begin, end) of one row.  MODE is the row's mode; every warp of the block runs this with
-// the same arguments.
-template <int VEC, bool PEN, int MODE>
-__device__ __forceinline__ void stream_slice(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
-                                             const float* __restrict__ row,
-                                             const uint8_t* __restrict__ seen_row, int begin, int end,
-                                             Tracked& t, Ring ring) {
-  Shared& sm = *c.sm;
-  const int tid = threadIdx.x, nt = blockDim.x;
-  const int off = P.vocab_offset;
-  constexpr bool SELECT = (MODE == M_SELECT_K || MODE == M_SELECT_MINP);
-  PHASE_BEGIN();
-  int from = begin;
-  if (SELECT) {
-    // the first `cap` elements go straight into the buffer
-    const int fill_end = min(end, begin + c.cap);
-    for (int i = begin + tid; i < fill_end; i += nt) {
-      float l = exact_logit<PEN>(P, rc, h, seen_row, i, row[i]);
-      if (rc.track && (l > t.gl || (l == t.gl && i < t.gid))) { t.gl = l; t.gid = i; }
-      float s = scaled(l, rc);
-      if (!(s == s)) s = neg_inf();
-      if (MODE == M_SELECT_MINP) t.mns = fminf(t.mns, s);
-      c.buf[i - begin] = make_key(s, (uint32_t)(i + off));
-    }
-    __syncthreads();
-    if (tid == 0) sm.n = fill_end - begin;
-    __syncthreads();
-    if (end > fill_end) buffer_rebuild(c, 0);
-    from = fill_end;
-  }
-  PHASE_MARK(1);
-  if (PEN && P.history) {
-    // the penalised tokens of this slice come from the history table, not from the stream: one
-    // scattered load each, so the hot loop below never sees a penalised logit
-    for (int base = 0; base < h.mask + 1; base += nt) {
-      const int slot = base + tid;
-      const int idx = (slot <= h.mask) ? h.keys[slot] : HASH_EMPTY;
-      bool want = false;
-      unsigned long long key = 0ull;
-      if (idx != HASH_EMPTY && idx >= from && idx < end) {
-        int count = h.counts[slot];
-        if (seen_row && seen_row[idx]) count = max(count, 1);
-        float l = penalised(row[idx], count, rc);
-        if (rc.track && (l > t.gl || (l == t.gl && idx < t.gid))) { t.gl = l; t.gid = idx; }
-        float s = scaled(l, rc);
-        if (MODE == M_SELECT_MINP) t.mns = fminf(t.mns, s);
-        if (MODE == M_ARGMAX_G) {
-          float d = s + gumbel(hashed_uniform((uint32_t)(idx + off), rc.rkey));
-          if (d > t.al || (d == t.al && idx < t.aid)) { t.al = d; t.aid = idx; }
-        }
-        want = s == s;
-        key = make_key(s, (uint32_t)(idx + off));
-      }
-      if (SELECT) {
-        buffer_push(c, want, key);
-        if (sm.overflow) break;
-      }
+      todo = redo;
     }
   }
-  PHASE_MARK(2);
-  if (VEC == 4 && MODE != M_SELECT_MINP && ring.stages > 0 && seen_row == nullptr) {
-    stream_ring<PEN, MODE>(P, rc, c, h, row, from, end, t, ring);
-    PHASE_MARK(3);
-    return;
-  }
-  if (MODE == M_SELECT_K) {
-    stream_top_k<VEC, PEN>(P, rc, c, h, row, seen_row, from, end, t);
-    PHASE_MARK(3);
-    return;
-  }
-  float tau = sm.tau;
-  float floor_l = logit_floor(tau, rc.tf);
-  bool stop = SELECT && sm.overflow;
-  const int stride = nt * VEC;
-  const int span = stride * UNROLL;
-  Chunk<VEC> cur, nxt;
-  if (!stop) load_chunk<VEC, PEN>(cur, row, seen_row, from + tid * VEC, stride, end);
-  for (int base = from; base < end && !stop; base += span) {
-    const int first = base + tid * VEC;
-    if (base + span < end) load_chunk<VEC, PEN>(nxt, row, seen_row, first + span, stride, end);
-    unsigned pm = 0u;    // elements that need the exact path
-    unsigned redo = 0u;  // elements whose entry did not fit the buffer
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int idx = first + u * stride;
-      unsigned flagged = 0u;  // seen bytes of this vector: its elements take the exact path
-      if (PEN) {
-        if (idx < end) {
-          if (P.history) {
-            // history tokens were handled from the table: blank them here
-            const int local = idx - begin;
-            const unsigned hb = (h.bitmap[local >> 5] >> (local & 31)) & ((1u << VEC) - 1u);
-            if (hb) {
-#pragma unroll
-              for (int e = 0; e < VEC; ++e)
-                if ((hb >> e) & 1u) cur.v[u * VEC + e] = quiet_nan();
-            }
-          }
-          flagged = cur.seen[u];
-        }
-      }
-      if (PEN && flagged) {
-        pm |= ((1u << VEC) - 1u) << (u * VEC);
-      } else {
-        float m4 = cur.v[u * VEC];
-#pragma unroll
-        for (int e = 1; e < VEC; ++e) m4 = fmaxf(m4, cur.v[u * VEC + e]);
-        if (MODE == M_SELECT_MINP) {
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) t.mnl = fminf(t.mnl, cur.v[u * VEC + e]);
-        }
-        if (rc.track && m4 > t.gl) {
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            float l = cur.v[u * VEC + e];
-            if (l > t.gl) { t.gl = l; t.gid = idx + e; }
-          }
-        }
-        if (MODE == M_ARGMAX_G) {
-          // score + gumbel can only win if score + the largest gumbel reaches the best so far
-          if (scaled(m4, rc) + GUMBEL_MAX >= t.al) {
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) {
-              float sc = scaled(cur.v[u * VEC + e], rc);
-              if (sc + GUMBEL_MAX >= t.al) {
-                float d = sc + gumbel(hashed_uniform((uint32_t)(idx + e + off), rc.rkey));
-                if (d > t.al) { t.al = d; t.aid = idx + e; }
-              }
-            }
-          }
-        } else if (SELECT && m4 >= floor_l) {
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            float l = cur.v[u * VEC + e];
-            if (l >= floor_l) {
-              float sc = scaled(l, rc);
-              if (sc >= tau) {
-                int slot = atomicAdd(&sm.n, 1);
-                if (slot < c.cap) c.buf[slot] = make_key(sc, (uint32_t)(idx + e + off));
-                else redo |= 1u << (u * VEC + e);
-              }
-            }
-          }
-        }
-      }
-    }
-    // the exact path, one element per lane per round; an element whose entry does not fit is
-    // redone after the block has rebuilt the buffer
-    int rounds = 0;
-    while (true) {
-      while (__any_sync(FULL, pm != 0u)) {
-        const bool have = pm != 0u;
-        const int q = have ? __ffs(pm) - 1 : 0;
-        pm &= pm - 1u;
-        const int idx = first + (q / VEC) * stride + (q % VEC);
-        bool want = false;
-        unsigned long long key = 0ull;
-        if (have && idx < end) {
-          float l = exact_logit<PEN>(P, rc, h, seen_row, idx, pick(cur.v, q));
-          if (rc.track && (l > t.gl || (l == t.gl && idx < t.gid))) { t.gl = l; t.gid = idx; }
-          float s = scaled(l, rc);
-          if (MODE == M_SELECT_MINP) t.mns = fminf(t.mns, s);
-          if (MODE == M_ARGMAX_G) {
-            if (s + GUMBEL_MAX >= t.al) {
-              float d = s + gumbel(hashed_uniform((uint32_t)(idx + off), rc.rkey));
-              if (d > t.al || (d == t.al && idx < t.aid)) { t.al = d; t.aid = idx; }
-            }
-          } else if (SELECT) {
-            want = s >= tau;
-            key = make_key(s, (uint32_t)(idx + off));
-          }
-        }
-        if (SELECT) {
-          const bool fit = warp_append(c.buf, &sm.n, c.cap, want, key);  // every lane calls it
-          if (want && !fit) redo |= 1u << q;
-        }
-      }
-      if (!SELECT) break;
-      // one barrier per step: did any warp run out of buffer?
-      if (!__syncthreads_or(redo != 0u)) break;
-      buffer_rebuild(c, 0);
-      tau = sm.tau;
-      floor_l = logit_floor(tau, rc.tf);
-      if (sm.overflow || ++rounds > 64) {
-        if (tid == 0) sm.overflow = 1;
-        stop = true;
-        break;
-      }
-      pm = redo;
-      redo = 0u;
-    }
-    cur = nxt;
-  }
-  PHASE_MARK(3);
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
@@ -882,7 +837,7 @@ struct SmemMap {
   Ctx* ctx;
   RowCfg* rc;
   unsigned long long* bars;
-  unsigned char* region;  // streaming: bitmap + hash table; finishing: float scratch
+  unsigned char* region;  // the history tokens' hash keys, then: their counts | the ring | finish scratch
 };
 
 __device__ __forceinline__ SmemMap smem_map(unsigned char* raw, int cap, int keep) {
@@ -903,21 +858,23 @@ static_assert(sizeof(Shared) <= 256 && sizeof(Ctx) <= 128 && sizeof(RowCfg) <= 1
 #ifndef LEAT_MIN_BLOCKS
 #define LEAT_MIN_BLOCKS 2
 #endif
-template <int VEC, bool PEN>
+template <bool PEN>
 __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const KParams P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const SmemMap M = smem_map(smem_raw, P.cap, P.keep);
   unsigned long long* buf = M.buf;
   Shared& sm = *M.sm;
-  unsigned* bitmap = reinterpret_cast<unsigned*>(M.region);
-  int* hkeys = reinterpret_cast<int*>(bitmap + P.bm_words);
-  int* hcnt = hkeys + P.ht_size;
-  float* fw = reinterpret_cast<float*>(M.region);
+  // the hash keys stay until the last rebuild; their counts share bytes with the ring and with
+  // the scratch of the finish, which come later
+  int* hkeys = reinterpret_cast<int*>(M.region);
+  unsigned char* later = M.region + (((size_t)P.ht_size * 4 + 127) / 128) * 128;
+  int* hcnt = reinterpret_cast<int*>(later);
+  float* fw = reinterpret_cast<float*>(later);
   float* fi = fw + P.cap;
   float* fs = fi + P.cap;
   // the ring shares its bytes with the hash table, which is dead once the history pass is over
   Ring ring;
-  ring.data = reinterpret_cast<float*>(M.region + (((size_t)P.bm_words * 4 + 127) / 128) * 128);
+  ring.data = reinterpret_cast<float*>(later);
   ring.bars = M.bars;
   ring.stages = P.ring_stages;
 
@@ -936,7 +893,8 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const KPar
     c.buf = buf; c.stage = M.stage; c.hist = M.hist; c.sm = M.sm;
     c.cap = P.cap; c.keep = P.keep; c.mode = rc.mode; c.k = rc.k_eff; c.logm = rc.logm;
     c.divide = rc.divide; c.off = P.vocab_offset; c.begin = begin; c.rinv = rc.rinv; c.tf = rc.tf;
-    c.bitmap = (PEN && P.history) ? bitmap : nullptr;
+    c.hkeys = (PEN && P.history) ? hkeys : nullptr;
+    c.hmask = P.ht_size - 1;
     c.region = (P.cap - P.keep) / (nt >> 5);
   }
   __syncthreads();
@@ -944,28 +902,42 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const KPar
 
   if (tid == 0) {
     sm.n = 0; sm.m = 0; sm.conv = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.best = 0ull; sm.gbest = 0ull;
+    sm.vmin = 0xFFFFFFFFu; sm.vmax = 0u; sm.valid = 0; sm.smin2 = 0xFFFFFFFFu; sm.rmin = 0xFFFFFFFFu; sm.rmax = 0u;
     sm.smin = 0xFFFFFFFFu; sm.is_last = (S == 1);
+    sm.share_greedy = 0u; sm.share_gumbel = 0u; sm.share_min = 0xFFFFFFFFu;
   }
+#pragma unroll 1
+  for (int i = tid; i < BINS; i += nt) M.hist[i] = 0u;
   History h;
-  h.bitmap = bitmap; h.keys = hkeys; h.counts = hcnt; h.mask = P.ht_size - 1; h.begin = begin;
+  h.keys = hkeys; h.counts = hcnt; h.mask = P.ht_size - 1; h.begin = begin;
   if (PEN && P.history) {
-    for (int i = tid; i < P.bm_words; i += nt) bitmap[i] = 0u;
+#pragma unroll 1
     for (int i = tid; i < P.ht_size; i += nt) { hkeys[i] = HASH_EMPTY; hcnt[i] = 0; }
   }
   __syncthreads();
   if (PEN && P.history) {
     const int hl = P.history_len ? min(P.history_len[b], P.history_cap) : P.history_cap;
     const int* hist_ids = P.history + (size_t)b * P.history_cap;
-    for (int i = tid; i < hl; i += nt) {
-      int id = hist_ids[i] - P.vocab_offset;
-      if (id >= begin && id < end) {
-        int local = id - begin;
-        atomicOr(&bitmap[local >> 5], 1u << (local & 31));
-        uint32_t slot = lowbias32((uint32_t)id) & h.mask;
-        for (int probe = 0; probe <= h.mask; ++probe) {
-          int old = atomicCAS(&hkeys[slot], HASH_EMPTY, id);
-          if (old == HASH_EMPTY || old == id) { atomicAdd(&hcnt[slot], 1); break; }
-          slot = (slot + 1) & h.mask;
+    constexpr int IB = 4;  // history ids loaded together per thread
+#pragma unroll 1
+    for (int base = 0; base < hl; base += nt * IB) {
+      int ids[IB];
+#pragma unroll
+      for (int j = 0; j < IB; ++j) {
+        const int i = base + j * nt + tid;
+        ids[j] = i < hl ? hist_ids[i] - P.vocab_offset : -1;
+      }
+#pragma unroll
+      for (int j = 0; j < IB; ++j) {
+        const int id = ids[j];
+        if (id >= begin && id < end) {
+          uint32_t slot = lowbias32((uint32_t)id) & h.mask;
+#pragma unroll 1
+          for (int probe = 0; probe <= h.mask; ++probe) {
+            int old = atomicCAS(&hkeys[slot], HASH_EMPTY, id);
+            if (old == HASH_EMPTY || old == id) { atomicAdd(&hcnt[slot], 1); break; }
+            slot = (slot + 1) & h.mask;
+          }
         }
       }
     }
@@ -977,10 +949,17 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const KPar
   Tracked t;
   t.gl = neg_inf(); t.gid = NO_ID; t.al = neg_inf(); t.aid = NO_ID;
   t.mnl = __uint_as_float(0x7F800000u); t.mns = t.mnl;
-  if (mode == M_ARGMAX_L) stream_slice<VEC, PEN, M_ARGMAX_L>(P, rc, c, h, row, seen_row, begin, end, t, ring);
-  else if (mode == M_ARGMAX_G) stream_slice<VEC, PEN, M_ARGMAX_G>(P, rc, c, h, row, seen_row, begin, end, t, ring);
-  else if (mode == M_SELECT_K) stream_slice<VEC, PEN, M_SELECT_K>(P, rc, c, h, row, seen_row, begin, end, t, ring);
-  else if (mode == M_SELECT_MINP) stream_slice<VEC, PEN, M_SELECT_MINP>(P, rc, c, h, row, seen_row, begin, end, t, ring);
+  if (mode != M_GENERAL) {
+    const bool select = mode == M_SELECT_K || mode == M_SELECT_MINP;
+    int from = begin;
+    if (select) from = slice_fill<PEN>(P, rc, c, h, row, seen_row, begin, end, t);
+    PHASE_MARK(1);
+    if (PEN && P.history) slice_history<PEN>(P, rc, c, h, row, seen_row, from, end, t);
+    PHASE_MARK(2);
+    if (ring.stages > 0) stream_ring<PEN>(P, rc, c, h, row, seen_row, from, end, t, ring);
+    else stream_plain<PEN>(P, rc, c, h, row, seen_row, from, end, t);
+    PHASE_MARK(3);
+  }
   __syncthreads();
 
 #ifdef LEAT_PHASE_CLOCKS
@@ -1007,7 +986,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const KPar
   __syncthreads();
   if ((mode == M_SELECT_K || mode == M_SELECT_MINP) && !sm.overflow) {
     // the stream of a top-k row leaves raw entries behind: the rebuild also turns them into keys
-    buffer_rebuild(c, mode == M_SELECT_K);
+    buffer_rebuild(c, 1);
   }
   bool failed = (mode == M_GENERAL) || sm.overflow;
 
@@ -1018,6 +997,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const KPar
     if ((mode == M_SELECT_K || mode == M_SELECT_MINP) && !failed) {
       const int n = sm.n;
       unsigned long long* dst = P.ws_keys + cell * P.keep;
+#pragma unroll 1
       for (int i = tid; i < n; i += nt) dst[i] = buf[i];
     }
     if (tid == 0) {
@@ -1043,6 +1023,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const KPar
     unsigned long long g = 0ull, a = 0ull;
     unsigned mnb = 0xFFFFFFFFu;
     int bad = 0;
+#pragma unroll 1
     for (int j = tid; j < S; j += nt) {
       const size_t c2 = (size_t)b * S + j;
       unsigned long long gj = __ldcg(&P.ws_best[c2 * 2 + 0]), aj = __ldcg(&P.ws_best[c2 * 2 + 1]);
@@ -1058,6 +1039,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const KPar
     failed = __syncthreads_or(bad) != 0;
     if ((mode == M_SELECT_K || mode == M_SELECT_MINP) && !failed) {
       const int total_slots = S * P.keep;
+#pragma unroll 1
       for (int base = 0; base < total_slots; base += nt) {
         int i = base + tid;
         int j = i / P.keep, q = i - j * P.keep;
@@ -1085,6 +1067,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const KPar
     if (!failed && (mode == M_SELECT_K || mode == M_SELECT_MINP)) {
       n = sm.n;
       if (n > cap) { n = 0; failed = true; }
+#pragma unroll 1
       for (int i = tid; i < n; i += nt) {
         P.cand_value[(size_t)b * cap + i] = key_value(buf[i]);
         P.cand_id[(size_t)b * cap + i] = key_id(buf[i]);
@@ -1127,14 +1110,18 @@ __global__ void __launch_bounds__(512) finish_candidates_kernel(const KParams P)
   Ctx c;
   c.buf = buf; c.stage = M.stage; c.hist = M.hist; c.sm = M.sm;
   c.cap = P.cap; c.keep = P.keep; c.mode = mode; c.k = rc.k_eff; c.logm = rc.logm;
-  c.divide = 0; c.off = 0; c.begin = 0; c.rinv = 1.0f; c.tf = 1.0f; c.bitmap = nullptr; c.region = 1;
+  c.divide = 0; c.off = 0; c.begin = 0; c.rinv = 1.0f; c.tf = 1.0f; c.hkeys = nullptr; c.hmask = 0; c.region = 1;
   if (tid == 0) {
     sm.n = 0; sm.m = 0; sm.conv = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.best = 0ull; sm.gbest = 0ull;
+    sm.vmin = 0xFFFFFFFFu; sm.vmax = 0u; sm.valid = 0; sm.smin2 = 0xFFFFFFFFu; sm.rmin = 0xFFFFFFFFu; sm.rmax = 0u;
     sm.smin = 0u;
   }
+#pragma unroll 1
+  for (int i = tid; i < BINS; i += nt) M.hist[i] = 0u;
   __syncthreads();
   unsigned long long g = 0ull;
   int bad = 0;
+#pragma unroll 1
   for (int j = tid; j < parts; j += nt) {
     unsigned long long gj = P.g_best[(size_t)j * rows + b];
     g = gj > g ? gj : g;
@@ -1146,6 +1133,7 @@ __global__ void __launch_bounds__(512) finish_candidates_kernel(const KParams P)
   if (tid == 0 && P.out_greedy) P.out_greedy[b] = key_id(sm.gbest);
   if (!failed && mode == M_ARGMAX_G) {
     unsigned long long a = 0ull;
+#pragma unroll 1
     for (int j = tid; j < parts; j += nt) {
       size_t at = ((size_t)j * rows + b) * cap;
       unsigned long long kk = make_key(P.g_value[at], (uint32_t)P.g_id[at]);
@@ -1157,6 +1145,7 @@ __global__ void __launch_bounds__(512) finish_candidates_kernel(const KParams P)
   }
   if (!failed && (mode == M_SELECT_K || mode == M_SELECT_MINP)) {
     const int total_slots = parts * cap;
+#pragma unroll 1
     for (int base = 0; base < total_slots; base += nt) {
       int i = base + tid;
       int j = i / cap, q = i - j * cap;
@@ -1195,10 +1184,12 @@ __global__ void verify_kernel(const int* __restrict__ drafted, const int* __rest
   const int ran = drafts + 1;
   const int* against = greedy ? greedy : sampled;
   int kept = drafts;
+#pragma unroll 1
   for (int j = 0; j < drafts; ++j) {
     if (drafted[(size_t)i * drafts + j] != against[(size_t)i * ran + j]) { kept = j; break; }
   }
   accepted[i] = kept;
+#pragma unroll 1
   for (int j = 0; j < ran; ++j) {
     int t = -1;
     if (j < kept) t = greedy ? drafted[(size_t)i * drafts + j] : sampled[(size_t)i * ran + j];

@@ -41,6 +41,7 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t 
 }
 // false if the copy has not landed after about a million polls (far beyond any real latency)
 __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint32_t parity) {
+#pragma unroll 1
   for (int spin = 0; spin < (1 << 20); ++spin)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
@@ -64,28 +65,66 @@ struct Ring {
   int stages;
 };
 
-// MODE is M_SELECT_K, M_ARGMAX_L or M_ARGMAX_G.  Streams [from, end) of `row`; `from` and the row
-// are 16-byte aligned and end - from is a multiple of 4.
-template <bool PEN, int MODE>
+// One lane's look at a logit the cheap tests singled out: penalties if a dense seen mask marks it,
+// greedy tracking, and whether it goes on to the candidate buffer.  Kept out of line: it runs for a
+// few logits per step and must not bloat the loop around it.
+template <bool PEN>
+__device__ __noinline__ void ring_visit(const KParams& P, const RowCfg& rc, const History& h, Shared& sm,
+                                        const uint8_t* seen_row, Tracked& t, int idx, float raw, int what) {
+  // what: 1 = greedy candidate, 2 = whole-row gumbel candidate, 4 = smallest-score candidate
+  bool in_history = false;
+  if (PEN && P.history) in_history = leat::in_history(h.keys, h.mask, idx);
+  if (in_history) return;  // its penalised logit came from the history table
+  float l = raw;
+  if (PEN && seen_row && seen_row[idx]) l = penalised(raw, 1, rc);
+  if ((what & 1) && (l > t.gl || (l == t.gl && idx < t.gid))) {
+    t.gl = l; t.gid = idx;
+    atomicMax(&sm.share_greedy, ord32(l + 0.0f));
+  }
+  if (what & 2) {
+    const float sc = scaled(l, rc);
+    if (sc + GUMBEL_MAX >= t.al) {
+      const float d = sc + gumbel(hashed_uniform((uint32_t)(idx + P.vocab_offset), rc.rkey));
+      if (d > t.al || (d == t.al && idx < t.aid)) {
+        t.al = d; t.aid = idx;
+        atomicMax(&sm.share_gumbel, ord32(d + 0.0f));
+      }
+    }
+  }
+  if (what & 4) {
+    t.mns = fminf(t.mns, scaled(l, rc));
+    t.mnl = fminf(t.mnl, l);
+    atomicMin(&sm.share_min, ord32(l + 0.0f));
+  }
+}
+
+// Streams [from, end) of `row` in the row's mode (rc.mode: M_SELECT_K, M_SELECT_MINP, M_ARGMAX_L or
+// M_ARGMAX_G).  `row + from` is 16-byte aligned and end - from is a multiple of 4.
+template <bool PEN>
 __device__ __noinline__ void stream_ring(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
-                                         const float* __restrict__ row, int from, int end, Tracked& t,
-                                         Ring ring) {
+                                         const float* __restrict__ row, const uint8_t* __restrict__ seen_row,
+                                         int from, int end, Tracked& t, Ring ring) {
   Shared& sm = *c.sm;
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
   constexpr int N = RING_PER_THREAD;
-  constexpr bool SELECT = MODE == M_SELECT_K;
-  const int off = P.vocab_offset;
+  const int mode = rc.mode;
+  const bool select = mode == M_SELECT_K || mode == M_SELECT_MINP;
+  const bool greedy = mode == M_ARGMAX_L || rc.track != 0;
+  const bool dense = PEN && seen_row != nullptr;
+  const bool want_hi = greedy || mode == M_ARGMAX_G, want_lo = mode == M_SELECT_MINP;
   const int stage_elems = nt * N;
   const int steps = (end - from + stage_elems - 1) / stage_elems;
   const int stride = nt * 4;
 
   if (tid == 0) {
+#pragma unroll 1
     for (int s = 0; s < ring.stages; ++s) mbar_init(&ring.bars[s], 1);
     mbar_fence_init();
   }
-  if (SELECT) {
+  if (select) {
     // keys so far fit the first `keep` slots; the rest of the buffer is one raw region per warp
     if (sm.n > c.keep) buffer_rebuild(c, 0);
+#pragma unroll 1
     for (int i = sm.n + tid; i < c.keep; i += nt) c.buf[i] = 0ull;
     if (tid < 32) sm.wcount[tid] = 0;
     if (tid == 0) sm.conv = sm.n;
@@ -95,6 +134,7 @@ __device__ __noinline__ void stream_ring(const KParams& P, const RowCfg& rc, con
   {
     const int first = min(ring.stages, steps);
     if (tid == 0) {
+#pragma unroll 1
       for (int s = 0; s < first; ++s) {
         const int at = from + s * stage_elems;
         const uint32_t bytes = (uint32_t)(min(end, at + stage_elems) - at) * 4u;
@@ -107,74 +147,99 @@ __device__ __noinline__ void stream_ring(const KParams& P, const RowCfg& rc, con
   const int region = c.region;
   unsigned long long* const mine = c.buf + c.keep + warp * region;
   int held = 0;
-  float floor_l = SELECT ? logit_floor(sm.tau, rc.tf) : 0.0f;
-  bool stop = SELECT && sm.overflow != 0;
+  float floor_l = select ? logit_floor(sm.tau, rc.tf) : __uint_as_float(0x7F800000u);
+  bool stop = select && sm.overflow != 0;
   int it = 0;
+#pragma unroll 1
   for (; it < steps && !stop; ++it) {
     RING_CLOCK(a0);
     const int s = it % ring.stages;
     const bool landed = mbar_wait_bounded(&ring.bars[s], (uint32_t)(it / ring.stages) & 1u);
     RING_CLOCK(a1);
-    const int base = from + it * stage_elems;
-    const int first = base + tid * 4;
+    const int first = from + it * stage_elems + tid * 4;
     const float* stage = ring.data + (size_t)s * stage_elems;
     const float4* src = reinterpret_cast<const float4*>(stage) + tid;
-    // sixteen logits: kept only as a mask of those at or above the floor, and their maximum
-    unsigned pm = 0u;
-    float m = neg_inf();
+    // sixteen logits, kept only as: which reach the floor, which a dense mask marks, max and min
+    unsigned pm = 0u, xm = 0u;
+    float hi = neg_inf(), lo = __uint_as_float(0x7F800000u);
 #pragma unroll
     for (int u = 0; u < N / 4; ++u) {
       float4 x = make_float4(quiet_nan(), quiet_nan(), quiet_nan(), quiet_nan());
-      if (landed && first + u * stride < end) x = src[u * nt];
-      if (SELECT) {
-        pm |= (x.x >= floor_l ? 1u : 0u) << (u * 4 + 0);
-        pm |= (x.y >= floor_l ? 1u : 0u) << (u * 4 + 1);
-        pm |= (x.z >= floor_l ? 1u : 0u) << (u * 4 + 2);
-        pm |= (x.w >= floor_l ? 1u : 0u) << (u * 4 + 3);
-      }
-      if (MODE != M_SELECT_K || rc.track) m = fmaxf(fmaxf(m, fmaxf(x.x, x.y)), fmaxf(x.z, x.w));
-    }
-    // greedy tracking: the largest raw logit that no history entry penalises
-    if ((MODE == M_ARGMAX_L || rc.track) && m > t.gl) {
-      for (int q = 0; q < N; ++q) {
-        const int idx = first + (q >> 2) * stride + (q & 3);
-        const float l = idx < end ? stage[(q >> 2) * stride + tid * 4 + (q & 3)] : quiet_nan();
-        if (l > t.gl) {
-          bool penalised_elsewhere = false;
-          if (PEN && P.history) {
-            const int local = idx - h.begin;
-            penalised_elsewhere = (h.bitmap[local >> 5] >> (local & 31)) & 1u;
-          }
-          if (!penalised_elsewhere) { t.gl = l; t.gid = idx; }
+      const bool in = landed && first + u * stride < end;
+      if (in) x = src[u * nt];
+      pm |= (x.x >= floor_l ? 1u : 0u) << (u * 4 + 0);
+      pm |= (x.y >= floor_l ? 1u : 0u) << (u * 4 + 1);
+      pm |= (x.z >= floor_l ? 1u : 0u) << (u * 4 + 2);
+      pm |= (x.w >= floor_l ? 1u : 0u) << (u * 4 + 3);
+      if (want_hi) hi = fmaxf(fmaxf(hi, fmaxf(x.x, x.y)), fmaxf(x.z, x.w));
+      if (want_lo) lo = fminf(fminf(lo, fminf(x.x, x.y)), fminf(x.z, x.w));
+      if (dense && in) {
+        const unsigned bytes = *reinterpret_cast<const unsigned*>(seen_row + first + u * stride);
+        if (bytes) {
+          xm |= ((bytes & 0xFFu) ? 1u : 0u) << (u * 4 + 0);
+          xm |= ((bytes & 0xFF00u) ? 1u : 0u) << (u * 4 + 1);
+          xm |= ((bytes & 0xFF0000u) ? 1u : 0u) << (u * 4 + 2);
+          xm |= ((bytes & 0xFF000000u) ? 1u : 0u) << (u * 4 + 3);
         }
       }
     }
-    // score + gumbel can only win if score + the largest gumbel reaches the best so far
-    if (MODE == M_ARGMAX_G && scaled(m, rc) + GUMBEL_MAX >= t.al) {
+    // logits that may beat the greedy best, the whole-row gumbel best or the smallest score so far
+    // The bounds are the block's, not the thread's: a thread's own best rises with every few
+    // logits it sees, the block's only a dozen times per slice.  Ties with the bound still count
+    // (the lower index wins), hence >= and <=.
+    int what = 0;
+    float bound_g = 0.0f, bound_a = 0.0f, bound_m = 0.0f;
+    if (greedy) {
+      bound_g = unord32(*reinterpret_cast<volatile unsigned*>(&sm.share_greedy));
+      if (!(bound_g == bound_g)) bound_g = neg_inf();
+      if (hi >= bound_g) what |= 1;
+    }
+    if (mode == M_ARGMAX_G) {
+      bound_a = unord32(*reinterpret_cast<volatile unsigned*>(&sm.share_gumbel));
+      if (!(bound_a == bound_a)) bound_a = neg_inf();
+      if (scaled(hi, rc) + GUMBEL_MAX >= bound_a) what |= 2;
+    }
+    if (mode == M_SELECT_MINP) {
+      bound_m = unord32(*reinterpret_cast<volatile unsigned*>(&sm.share_min));
+      if (!(bound_m == bound_m)) bound_m = __uint_as_float(0x7F800000u);
+      if (lo <= bound_m) what |= 4;
+    }
+    if (what) {
+#pragma unroll 1
       for (int q = 0; q < N; ++q) {
-        const int idx = first + (q >> 2) * stride + (q & 3);
-        const float l = idx < end ? stage[(q >> 2) * stride + tid * 4 + (q & 3)] : quiet_nan();
-        const float sc = scaled(l, rc);
-        if (sc + GUMBEL_MAX >= t.al) {
-          bool penalised_elsewhere = false;
-          if (PEN && P.history) {
-            const int local = idx - h.begin;
-            penalised_elsewhere = (h.bitmap[local >> 5] >> (local & 31)) & 1u;
-          }
-          if (!penalised_elsewhere) {
-            const float d = sc + gumbel(hashed_uniform((uint32_t)(idx + off), rc.rkey));
-            if (d > t.al) { t.al = d; t.aid = idx; }
-          }
+        const int at = (q >> 2) * stride + (q & 3);
+        if (first + at < end && !((xm >> q) & 1u)) {
+          const float raw = stage[at + tid * 4];
+          if (((what & 1) && raw >= bound_g) || ((what & 2) && scaled(raw, rc) + GUMBEL_MAX >= bound_a) ||
+              ((what & 4) && raw <= bound_m))
+            ring_visit<PEN>(P, rc, h, sm, seen_row, t, first + at, raw, what);
         }
+      }
+    }
+    // what goes to the candidate buffer: logits at the floor, but under a dense mask only if the
+    // penalised logit still reaches it
+    unsigned am = select ? (pm & ~xm) : 0u;
+    if (dense && xm) {
+      const int all = (greedy ? 1 : 0) | (mode == M_ARGMAX_G ? 2 : 0) | (mode == M_SELECT_MINP ? 4 : 0);
+      unsigned left = xm;
+      while (left) {
+        const int q = __ffs(left) - 1;
+        left &= left - 1u;
+        const int at = (q >> 2) * stride + (q & 3);
+        const float raw = stage[at + tid * 4];
+        if (all) ring_visit<PEN>(P, rc, h, sm, seen_row, t, first + at, raw, all);
+        bool in_history = false;
+        if (P.history) in_history = leat::in_history(h.keys, h.mask, first + at);
+        if (select && !in_history && penalised(raw, 1, rc) >= floor_l) am |= 1u << q;
       }
     }
     int rounds = 0;
     while (true) {
       unsigned redo = 0u;
-      if (SELECT && __any_sync(FULL, pm != 0u)) {
-        // the warp's passing logits go to its own region: no atomics, one scan over the lanes;
-        // each lane then walks its own few set bits and fetches the logit back from the stage
-        const int count = __popc(pm);
+      if (select && __any_sync(FULL, am != 0u)) {
+        // the warp's entries go to its own region: no atomics, one scan over the lanes; each lane
+        // then walks its own few set bits and fetches the logit back from the stage
+        const int count = __popc(am);
         int incl = count;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
@@ -183,13 +248,14 @@ __device__ __noinline__ void stream_ring(const KParams& P, const RowCfg& rc, con
         }
         const int total = __shfl_sync(FULL, incl, 31);
         int slot = held + incl - count;
-        unsigned left = pm;
+        unsigned left = am;
         while (left) {
           const int q = __ffs(left) - 1;
           left &= left - 1u;
           if (slot < region) {
             const int at = (q >> 2) * stride + (q & 3);
-            const float l = stage[at + tid * 4];
+            float l = stage[at + tid * 4];
+            if (dense && ((xm >> q) & 1u)) l = penalised(l, 1, rc);
             mine[slot] = ((unsigned long long)__float_as_uint(l) << 32) | (uint32_t)(first + at);
           } else {
             redo |= 1u << q;
@@ -223,11 +289,13 @@ __device__ __noinline__ void stream_ring(const KParams& P, const RowCfg& rc, con
         break;
       }
       // what did not fit is taken again from the stage, against the new floor
-      pm = 0u;
+      am = 0u;
       while (redo) {
         const int q = __ffs(redo) - 1;
         redo &= redo - 1u;
-        if (stage[(q >> 2) * stride + tid * 4 + (q & 3)] >= floor_l) pm |= 1u << q;
+        float l = stage[(q >> 2) * stride + tid * 4 + (q & 3)];
+        if (dense && ((xm >> q) & 1u)) l = penalised(l, 1, rc);
+        if (l >= floor_l) am |= 1u << q;
       }
     }
     // the stage is free: start the copy of the step that will use it next
@@ -245,6 +313,7 @@ __device__ __noinline__ void stream_ring(const KParams& P, const RowCfg& rc, con
     }
   }
   // copies still in flight (the loop stopped early) must land before the ring is reused
+#pragma unroll 1
   for (int j = it; j < issued; ++j)
     mbar_wait_bounded(&ring.bars[j % ring.stages], (uint32_t)(j / ring.stages) & 1u);
   __syncthreads();
