@@ -1,0 +1,126 @@
+"""GPU parity of the vocabulary-sharded entry points (emulated on one GPU: the slices of N ranks
+are selected one after the other, laid out as an all-gather would leave them, and finished once),
+of the dense `seen` mask on the streaming path, and of the draft-verification kernel."""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+def _sharded_on_one_gpu(device, w, parts, mode, cap=128, k_max=64, width=64):
+    import torch
+
+    from leat_b200 import _lib, workloads
+    from leat_b200.sampler import Sampled, Sampler, _stream
+
+    t = lambda x: None if x is None else torch.as_tensor(x).to(device)  # noqa: E731
+    rows, vocab = w.rows, w.vocab
+    widest = max(b - a for a, b in (workloads.shard_bounds(vocab, parts, r) for r in range(parts)))
+    sampler = Sampler(rows, max(widest, 8), k_max, device)
+    seed = torch.as_tensor(w.seed.astype(np.int64)).to(device).to(torch.uint32)
+    options, penalties, history, uniform, position = t(w.options), t(w.penalties), t(w.history), t(w.uniform), t(w.position)
+    value = torch.zeros((parts, rows, cap), dtype=torch.float32, device=device)
+    ids = torch.zeros((parts, rows, cap), dtype=torch.int32, device=device)
+    count = torch.zeros((parts, rows), dtype=torch.int32, device=device)
+    best = torch.zeros((parts, rows), dtype=torch.int64, device=device)
+    for r in range(parts):
+        start, stop = workloads.shard_bounds(vocab, parts, r)
+        part = torch.as_tensor(np.ascontiguousarray(w.logits[:, start:stop])).to(device)
+        a, keep = sampler._args(part, options, seed, position, None, history, None, penalties,
+                                uniform if mode == "U" else None, 0, start, vocab)  # fmt: skip
+        _lib.check(_lib.lib.leat_topk_local(sampler.handle, C.byref(a), value[r].data_ptr(), ids[r].data_ptr(),
+                                            count[r].data_ptr(), best[r].data_ptr(), cap, _stream()), "leat_topk_local")  # fmt: skip
+        torch.cuda.synchronize()
+        assert int(count[r].min()) >= 0
+    dummy = torch.empty((rows, 4), dtype=torch.float32, device=device)
+    a, keep = sampler._args(dummy, options, seed, position, None, None, None, None, uniform if mode == "U" else None, 0)
+    a.vocab, a.vocab_total = vocab, vocab
+    out = Sampled(torch.empty((rows, 1), dtype=torch.int32, device=device),
+                  status=torch.zeros(1, dtype=torch.int32, device=device))
+    out.greedy = torch.empty(rows, dtype=torch.int32, device=device)
+    out.cut = torch.empty(rows, dtype=torch.float32, device=device)
+    out.kept = torch.empty(rows, dtype=torch.int32, device=device)
+    out.probs = torch.empty((rows, width), dtype=torch.float32, device=device)
+    out.prob_ids = torch.empty((rows, width), dtype=torch.int32, device=device)
+    a.out_ids, a.status, a.out_greedy = out.ids.data_ptr(), out.status.data_ptr(), out.greedy.data_ptr()
+    a.out_cut, a.out_kept = out.cut.data_ptr(), out.kept.data_ptr()
+    a.out_probs, a.out_prob_ids, a.out_width = out.probs.data_ptr(), out.prob_ids.data_ptr(), width
+    _lib.check(_lib.lib.leat_sample_from_candidates(sampler.handle, C.byref(a), value.data_ptr(), ids.data_ptr(),
+                                                    count.data_ptr(), best.data_ptr(), parts, cap, _stream()),
+               "leat_sample_from_candidates")  # fmt: skip
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("parts", [2, 4, 8])
+@pytest.mark.parametrize("mode", ["U", "G"])
+def test_sharded_equals_single_device_oracle(device, parts, mode):
+    from leat_b200 import workloads
+
+    w = workloads.config5(rows=24, vocab=201088)
+    w.options[3, 0] = 0.0  # a greedy row among them
+    got = _sharded_on_one_gpu(device, w, parts, mode)
+    want = helpers.oracle_run(w, mode)
+    helpers.compare(want, got, 64, max_fragile=1)
+
+
+def test_dense_seen_mask_on_the_streaming_path(device):
+    """leat's own form of the penalty input: a (B, V) bool mask, here on a vocabulary large enough
+    to take the streaming path, with and without a history beside it."""
+    import torch
+
+    from leat_b200 import workloads
+    from leat_b200.sampler import Sampler
+    from oracle import sampler_oracle as oracle
+
+    w = workloads.config2(rows=6, vocab=151936)
+    rng = np.random.default_rng(7)
+    seen = np.zeros((w.rows, w.vocab), bool)
+    for b in range(w.rows):
+        seen[b, rng.integers(0, w.vocab, 700)] = True
+        seen[b, np.argsort(-w.logits[b])[:5]] = True  # the likeliest tokens too
+    w.options[:, 4] = 1.3  # presence penalty
+    w.options[2, 0] = 0.0  # a greedy row
+    sampler = Sampler(w.rows, w.vocab, 256, device)
+    t = lambda x: torch.as_tensor(x).to(device)  # noqa: E731
+    seed = torch.as_tensor(w.seed.astype(np.int64)).to(device).to(torch.uint32)
+    for history in (None, w.history):
+        penalties = None if history is None else w.penalties
+        got = sampler.sample_full(t(w.logits), t(w.options), seed, t(w.position), t(seen),
+                                  history=None if history is None else t(history),
+                                  penalties=None if penalties is None else t(penalties),
+                                  uniform=t(w.uniform), width=128, want_greedy=True, want_cut=True)  # fmt: skip
+        want = oracle.sample(w.logits, w.options, w.seed, w.position, seen, history=history, penalties=penalties,
+                             uniform_draws=w.uniform, order="block")  # fmt: skip
+        helpers.compare(want, got, 128, max_fragile=0)
+
+
+def test_verify_draft_accepts_and_rejects(device):
+    import torch
+
+    from leat_b200 import speculative
+    from oracle import sampler_oracle as oracle
+
+    rng = np.random.default_rng(3)
+    sampled = rng.integers(0, 50, (16, 9)).astype(np.int32)
+    drafted = sampled[:, :8].copy()
+    for i in range(16):  # sequence i keeps i % 9 drafts
+        if i % 9 < 8:
+            drafted[i, i % 9] += 1
+    greedy = sampled.copy()
+    greedy[:, 5] += 1
+    d, s, g = (torch.as_tensor(x).to(device) for x in (drafted, sampled, greedy))
+    accepted, tokens = speculative.verify_draft(d, s)
+    kept, toks = oracle.verify_draft(drafted, sampled)
+    np.testing.assert_array_equal(accepted.cpu().numpy(), kept)
+    np.testing.assert_array_equal(tokens.cpu().numpy(), toks)
+    assert kept.tolist() == [i % 9 for i in range(16)]
+    accepted, tokens = speculative.verify_draft(d, s, greedy=g)
+    kept, toks = oracle.verify_draft_greedy(drafted, greedy, sampled)
+    np.testing.assert_array_equal(accepted.cpu().numpy(), kept)
+    np.testing.assert_array_equal(tokens.cpu().numpy(), toks)
