@@ -192,8 +192,18 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
   P.slices = plan.slices; P.slice_len = plan.slice_len; P.bm_words = plan.bm_words; P.ht_size = plan.ht_size;
   P.ring_stages = plan.ring_stages;  // 0 unless rows are 16-byte aligned multiples of four floats
   int rc = pen ? launch_one<true>(P, plan, stream) : launch_one<false>(P, plan, stream);
-  if (rc == LEAT_OK) h->launches += 1;
-  return rc;
+  if (rc != LEAT_OK) return rc;
+  h->launches += 1;
+  // rows the single pass flagged are finished by the exact multi-pass kernel; its blocks return at
+  // once for every other row
+  if (!(P.flags & 2u) && !P.cand_count) {
+    const int shared = (int)(G_BINS * 12 + 384 + (size_t)plan.ht_size * 8);
+    if (pen) general_kernel<true><<<P.rows, 512, shared, stream>>>(P);
+    else general_kernel<false><<<P.rows, 512, shared, stream>>>(P);
+    if (cuda_failed(cudaGetLastError(), "general_kernel launch")) return LEAT_E_CUDA;
+    h->launches += 1;
+  }
+  return LEAT_OK;
 }
 
 template <typename K>
@@ -233,6 +243,7 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
   h->sm_count = sms > 0 ? sms : 148;
   const int most = 200 * 1024;
   if (allow_shared(sample_kernel<true>, most) || allow_shared(sample_kernel<false>, most) ||
+      allow_shared(general_kernel<true>, most) || allow_shared(general_kernel<false>, most) ||
       allow_shared(finish_candidates_kernel, most)) {
     delete h; return LEAT_E_CUDA;
   }
@@ -425,7 +436,8 @@ int static_setup(int device, StaticDevice** out) {
       return LEAT_E_CUDA;
     h.sm_count = sms > 0 ? sms : 148;
     const int most = 200 * 1024;
-    if (allow_shared(sample_kernel<true>, most) || allow_shared(sample_kernel<false>, most))
+    if (allow_shared(sample_kernel<true>, most) || allow_shared(sample_kernel<false>, most) ||
+        allow_shared(general_kernel<true>, most) || allow_shared(general_kernel<false>, most))
       return LEAT_E_CUDA;
     sd.ready = true;
   }

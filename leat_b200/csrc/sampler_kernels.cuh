@@ -1175,6 +1175,8 @@ __global__ void __launch_bounds__(512) finish_candidates_kernel(const KParams P)
   finish_row(P, rc, b, buf, sm, fw, fi, fs, neg_inf());
 }
 
+#include "general_kernel.cuh"
+
 // leat/engine.py:612-626 on the device: one thread per sequence
 __global__ void verify_kernel(const int* __restrict__ drafted, const int* __restrict__ sampled,
                               const int* __restrict__ greedy, int n, int drafts, int* accepted,
