@@ -168,7 +168,7 @@ __device__ inline void g_descend(const GRow& g, GShared& gs, unsigned* cnt, unsi
 }
 
 template <bool PEN>
-__global__ void __launch_bounds__(512) general_kernel(const KParams P) {
+__global__ void __launch_bounds__(512) general_kernel(const __grid_constant__ KParams P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned long long* mass = reinterpret_cast<unsigned long long*>(smem_raw);
   unsigned* cnt = reinterpret_cast<unsigned*>(mass + G_BINS);

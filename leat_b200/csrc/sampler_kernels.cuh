@@ -47,7 +47,7 @@ enum RowMode : int {
 
 constexpr int UNROLL = 4;  // vectors per thread per streaming step
 constexpr int BINS = 2048;  // buckets of one select step
-constexpr int SMEM_FIXED = 640;  // Shared (256 bytes), Ctx, RowCfg and the ring's mbarriers (128 bytes each)
+constexpr int SMEM_FIXED = 768;  // Shared (256 bytes), Ctx, RowCfg, the ring's mbarriers and History (128 bytes each)
 constexpr int MAX_RING_STAGES = 8;
 constexpr int HASH_EMPTY = -1;
 constexpr int NO_ID = 0x7FFFFFFF;
@@ -689,7 +689,7 @@ __device__ __noinline__ void slice_history(const KParams& P, const RowCfg& rc, c
   const int nt = blockDim.x, tid = threadIdx.x;
   const int mode = rc.mode;
   const bool select = mode == M_SELECT_K || mode == M_SELECT_MINP;
-  constexpr int HB = 8;  // table slots per thread per batch
+  constexpr int HB = 4;  // table slots per thread per batch (kept in registers)
 #pragma unroll 1
   for (int base = 0; base < h.mask + 1; base += nt * HB) {
     int idxs[HB], counts[HB];
@@ -705,7 +705,7 @@ __device__ __noinline__ void slice_history(const KParams& P, const RowCfg& rc, c
     }
     unsigned long long keys[HB];
     unsigned pending = 0u;
-#pragma unroll 1
+#pragma unroll
     for (int j = 0; j < HB; ++j) {
       const int idx = idxs[j];
       keys[j] = 0ull;
@@ -730,7 +730,7 @@ __device__ __noinline__ void slice_history(const KParams& P, const RowCfg& rc, c
       // one barrier per batch unless the buffer runs out
       int rounds = 0;
       while (true) {
-#pragma unroll 1
+#pragma unroll
         for (int j = 0; j < HB; ++j) {
           const bool fit = warp_append(c.buf, &sm.n, c.cap, (pending >> j) & 1u, keys[j]);
           if (fit) pending &= ~(1u << j);
@@ -738,7 +738,7 @@ __device__ __noinline__ void slice_history(const KParams& P, const RowCfg& rc, c
         if (!__syncthreads_or(pending != 0u)) break;
         buffer_rebuild(c, 0);
         if (sm.overflow || ++rounds > 64) break;
-#pragma unroll 1
+#pragma unroll
         for (int j = 0; j < HB; ++j)
           if (((pending >> j) & 1u) && !(key_value(keys[j]) >= sm.tau)) pending &= ~(1u << j);
       }
@@ -837,6 +837,7 @@ struct SmemMap {
   Ctx* ctx;
   RowCfg* rc;
   unsigned long long* bars;
+  History* history;
   unsigned char* region;  // the history tokens' hash keys, then: their counts | the ring | finish scratch
 };
 
@@ -850,6 +851,7 @@ __device__ __forceinline__ SmemMap smem_map(unsigned char* raw, int cap, int kee
   m.ctx = reinterpret_cast<Ctx*>(at + 256);
   m.rc = reinterpret_cast<RowCfg*>(at + 384);
   m.bars = reinterpret_cast<unsigned long long*>(at + 512);
+  m.history = reinterpret_cast<History*>(at + 640);
   m.region = at + SMEM_FIXED;
   return m;
 }
@@ -859,7 +861,7 @@ static_assert(sizeof(Shared) <= 256 && sizeof(Ctx) <= 128 && sizeof(RowCfg) <= 1
 #define LEAT_MIN_BLOCKS 2
 #endif
 template <bool PEN>
-__global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const KParams P) {
+__global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __grid_constant__ KParams P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const SmemMap M = smem_map(smem_raw, P.cap, P.keep);
   unsigned long long* buf = M.buf;
@@ -908,8 +910,8 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const KPar
   }
 #pragma unroll 1
   for (int i = tid; i < BINS; i += nt) M.hist[i] = 0u;
-  History h;
-  h.keys = hkeys; h.counts = hcnt; h.mask = P.ht_size - 1; h.begin = begin;
+  History& h = *M.history;  // in shared memory: the out-of-line stream functions take it by reference
+  if (tid == 0) { h.keys = hkeys; h.counts = hcnt; h.mask = P.ht_size - 1; h.begin = begin; }
   if (PEN && P.history) {
 #pragma unroll 1
     for (int i = tid; i < P.ht_size; i += nt) { hkeys[i] = HASH_EMPTY; hcnt[i] = 0; }
@@ -1095,7 +1097,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const KPar
 }
 
 // Finishes rows from candidates gathered from `g_parts` vocabulary slices: one block per row.
-__global__ void __launch_bounds__(512) finish_candidates_kernel(const KParams P) {
+__global__ void __launch_bounds__(512) finish_candidates_kernel(const __grid_constant__ KParams P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const SmemMap M = smem_map(smem_raw, P.cap, P.keep);
   unsigned long long* buf = M.buf;
