@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(512) general_kernel(const __grid_constant__ KP
   GRow g;
   g.P = &P; g.rc = &rc; g.row = P.logits + (size_t)b * P.row_stride; g.vocab = V;
   g.seen_row = (PEN && P.seen) ? P.seen + (size_t)b * P.seen_stride : nullptr;
-  g.h.keys = hkeys; g.h.counts = hcnt; g.h.mask = P.ht_size - 1; g.h.begin = 0;
+  g.h.raw = nullptr; g.h.keys = hkeys; g.h.counts = hcnt; g.h.mask = P.ht_size - 1; g.h.begin = 0;
   if (PEN && P.history) {
 #pragma unroll 1
     for (int i = tid; i < P.ht_size; i += nt) { hkeys[i] = HASH_EMPTY; hcnt[i] = 0; }

@@ -81,7 +81,7 @@ size_t shared_bytes(int cap, int keep, int bm_words, int ht_size, size_t ring = 
   (void)bm_words;
   // the hash keys, then one area shared by their counts, the ring and the scratch of the finish
   size_t keys = ((size_t)ht_size * 4 + 127) / 128 * 128;
-  size_t counts = (size_t)ht_size * 4;
+  size_t counts = (size_t)ht_size * 8;  // counts and the tokens' logits
   size_t finish = (size_t)cap * 8 + (size_t)(cap / 32) * 4;
   size_t later = counts > ring ? counts : ring;
   if (finish > later) later = finish;
@@ -115,14 +115,14 @@ Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool
   // the ring of bulk copies: as many stages as fit a block's share of shared memory
   p.ring_stages = 0;
   if (vec == 4 && !h->tune_no_ring) {
-    const size_t stage = (size_t)p.threads * 16 * 4;
+    const size_t stage = (size_t)p.threads * RING_PER_THREAD * 4;
     const size_t used = fixed_shared(h->cap, h->keep) + ((size_t)p.ht_size * 4 + 127) / 128 * 128;
     int stages = used < kSharedPerBlockTarget ? (int)((kSharedPerBlockTarget - used) / stage) : 0;
     if (h->tune_stages) stages = h->tune_stages;
     if (stages > MAX_RING_STAGES) stages = MAX_RING_STAGES;
     if (stages >= 2) p.ring_stages = stages;
   }
-  p.shared = (int)shared_bytes(h->cap, h->keep, p.bm_words, p.ht_size, (size_t)p.ring_stages * p.threads * 16 * 4);
+  p.shared = (int)shared_bytes(h->cap, h->keep, p.bm_words, p.ht_size, (size_t)p.ring_stages * p.threads * RING_PER_THREAD * 4);
   return p;
 }
 

@@ -602,6 +602,7 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
 // ---- streaming a slice --------------------------------------------------------------------------
 
 struct History {
+  const float* raw;  // the slice's history tokens' logits, loaded while the table was built
   const int* keys;
   const int* counts;
   int mask;
@@ -701,7 +702,7 @@ __device__ __noinline__ void slice_history(const KParams& P, const RowCfg& rc, c
       if (idx != HASH_EMPTY && !(idx >= from && idx < end)) idx = HASH_EMPTY;
       idxs[j] = idx;
       counts[j] = idx != HASH_EMPTY ? h.counts[slot] : 0;
-      raw[j] = idx != HASH_EMPTY ? row[idx] : 0.0f;
+      raw[j] = idx != HASH_EMPTY ? h.raw[slot] : 0.0f;
     }
     unsigned long long keys[HB];
     unsigned pending = 0u;
@@ -890,6 +891,8 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   // the row's options and the buffer's description live in shared memory, not in registers
   RowCfg& rc = *M.rc;
   Ctx& c = *M.ctx;
+  History& h = *M.history;  // in shared memory: the out-of-line stream functions take it by reference
+  float* hraw = reinterpret_cast<float*>(hcnt + P.ht_size);
   if (tid == 0) {
     rc = row_config(P, b);
     c.buf = buf; c.stage = M.stage; c.hist = M.hist; c.sm = M.sm;
@@ -898,46 +901,49 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     c.hkeys = (PEN && P.history) ? hkeys : nullptr;
     c.hmask = P.ht_size - 1;
     c.region = (P.cap - P.keep) / (nt >> 5);
-  }
-  __syncthreads();
-  const int mode = rc.mode;
-
-  if (tid == 0) {
     sm.n = 0; sm.m = 0; sm.conv = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.best = 0ull; sm.gbest = 0ull;
     sm.vmin = 0xFFFFFFFFu; sm.vmax = 0u; sm.valid = 0; sm.smin2 = 0xFFFFFFFFu; sm.rmin = 0xFFFFFFFFu; sm.rmax = 0u;
     sm.smin = 0xFFFFFFFFu; sm.is_last = (S == 1);
     sm.share_greedy = 0u; sm.share_gumbel = 0u; sm.share_min = 0xFFFFFFFFu;
+    h.raw = hraw; h.keys = hkeys; h.counts = hcnt; h.mask = P.ht_size - 1; h.begin = begin;
   }
+  // (the other threads clear the tables meanwhile)
 #pragma unroll 1
   for (int i = tid; i < BINS; i += nt) M.hist[i] = 0u;
-  History& h = *M.history;  // in shared memory: the out-of-line stream functions take it by reference
-  if (tid == 0) { h.keys = hkeys; h.counts = hcnt; h.mask = P.ht_size - 1; h.begin = begin; }
   if (PEN && P.history) {
 #pragma unroll 1
     for (int i = tid; i < P.ht_size; i += nt) { hkeys[i] = HASH_EMPTY; hcnt[i] = 0; }
   }
   __syncthreads();
+  const int mode = rc.mode;
   if (PEN && P.history) {
+    // the slice's history tokens: a hash table of counts, and each token's logit fetched now (one
+    // scattered load each, issued in batches) so the later passes never wait on them
     const int hl = P.history_len ? min(P.history_len[b], P.history_cap) : P.history_cap;
     const int* hist_ids = P.history + (size_t)b * P.history_cap;
-    constexpr int IB = 4;  // history ids loaded together per thread
+    constexpr int IB = 4;
 #pragma unroll 1
     for (int base = 0; base < hl; base += nt * IB) {
       int ids[IB];
+      float raw[IB];
 #pragma unroll
       for (int j = 0; j < IB; ++j) {
         const int i = base + j * nt + tid;
-        ids[j] = i < hl ? hist_ids[i] - P.vocab_offset : -1;
+        int id = i < hl ? hist_ids[i] - P.vocab_offset : -1;
+        if (!(id >= begin && id < end)) id = -1;
+        ids[j] = id;
       }
+#pragma unroll
+      for (int j = 0; j < IB; ++j) raw[j] = ids[j] >= 0 ? row[ids[j]] : 0.0f;
 #pragma unroll
       for (int j = 0; j < IB; ++j) {
         const int id = ids[j];
-        if (id >= begin && id < end) {
+        if (id >= 0) {
           uint32_t slot = lowbias32((uint32_t)id) & h.mask;
 #pragma unroll 1
           for (int probe = 0; probe <= h.mask; ++probe) {
             int old = atomicCAS(&hkeys[slot], HASH_EMPTY, id);
-            if (old == HASH_EMPTY || old == id) { atomicAdd(&hcnt[slot], 1); break; }
+            if (old == HASH_EMPTY || old == id) { atomicAdd(&hcnt[slot], 1); hraw[slot] = raw[j]; break; }
             slot = (slot + 1) & h.mask;
           }
         }

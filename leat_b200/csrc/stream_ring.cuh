@@ -30,12 +30,14 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                "l"(src), "r"(bytes), "r"(smem_addr(bar))
                : "memory");
 }
+// One poll; the thread may be suspended up to about a microsecond while the phase is pending, so
+// waiting warps leave the issue slots to the warps that have work.
 __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(ok)
-      : "r"(smem_addr(bar)), "r"(parity)
+      : "r"(smem_addr(bar)), "r"(parity), "r"(1000u)
       : "memory");
   return ok != 0u;
 }
@@ -57,7 +59,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint3
 #define RING_SET(x, y) do { } while (0)
 #endif
 
-constexpr int RING_PER_THREAD = 16;  // logits a thread takes from a stage
+#ifndef LEAT_RING_PER_THREAD
+#define LEAT_RING_PER_THREAD 16
+#endif
+constexpr int RING_PER_THREAD = LEAT_RING_PER_THREAD;  // logits a thread takes from a stage
 
 struct Ring {
   float* data;              // stages x (threads x 16) floats
