@@ -350,6 +350,28 @@ def run_sharded(args) -> None:
     ms = torch.tensor([a.elapsed_time(b) / args.steps], device=device)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms = float(ms.item())
+    # end to end: this rank's slice comes from pinned host memory every step, the ids go back
+    host_slice = torch.as_tensor(np.ascontiguousarray(w.logits[:, start:stop])).pin_memory()
+    host_ids = torch.empty((w.rows, 1), dtype=torch.int32).pin_memory()
+
+    def e2e_step(i):
+        pool[0].copy_(host_slice, non_blocking=True)
+        result = sharded.sample(pool[0], options, seed, position, history=history, penalties=penalties, uniform=uniform, out=out)
+        host_ids.copy_(result.ids, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    dist.barrier()
+    torch.cuda.synchronize()
+    a.record()
+    for i in range(args.steps):
+        e2e_step(i)
+    b.record()
+    torch.cuda.synchronize()
+    ms_e2e = torch.tensor([a.elapsed_time(b) / args.steps], device=device)
+    dist.all_reduce(ms_e2e, op=dist.ReduceOp.MAX)
+    ms_e2e = float(ms_e2e.item())
     if rank == 0:
         achieved = w.logit_bytes / world / (ms * 1e-3) / 1e9  # per GPU: each reads its slice once
         line = {
@@ -358,11 +380,14 @@ def run_sharded(args) -> None:
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD_NAMES[5], "rows": w.rows, "vocab": w.vocab, "parallelism": f"vocab{world}",
                        "draw": "supplied uniform", "l2": f"logits pool of {len(pool)} buffers per rank cycled, larger than L2",
-                       "exchange": "4 NCCL all-gathers of (score, id, count, greedy) candidates per step"},
+                       "exchange": "one NCCL all-gather of packed (score, id, count, greedy) candidate records per step",
+                       "timing": "CUDA events around the timed steps, launches issued from Python"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_kind": peak_kind, "kernel": "sample_kernel (per GPU, its vocabulary slice)",
                          "algorithmic_bytes_per_launch": w.logit_bytes // world},
-            "e2e": None, "gpu_launches": 2 * args.steps, "clocks": clocks.summary(),
+            "e2e": {"value": w.rows / (ms_e2e * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": int(host_slice.numel() * 4) * world,
+                    "d2h_bytes_per_step": w.rows * 4 * world},
+            "gpu_launches": 2 * args.steps, "clocks": clocks.summary(),
         }  # fmt: skip
         print(json.dumps(line), flush=True)
     dist.destroy_process_group()

@@ -186,6 +186,16 @@ int leat_sample_from_candidates(leat_sampler_t* handle, const leat_sample_args* 
                                 const int32_t* cand_count, const uint64_t* best, int32_t parts,
                                 int32_t cap, leat_stream_t stream);
 
+/* The same from packed records, so that one all-gather moves everything a rank hands over.  A
+   rank's record is leat_candidate_record_bytes(rows, cap) bytes: cand_value (rows, cap) float32 at
+   offset 0, then cand_id, cand_count and best at the offsets leat_candidate_record_layout()
+   returns (the caller points leat_topk_local at them).  `records` holds `parts` records back to
+   back, as the all-gather leaves them. */
+size_t leat_candidate_record_bytes(int32_t rows, int32_t cap);
+int leat_candidate_record_layout(int32_t rows, int32_t cap, size_t* id_at, size_t* count_at, size_t* best_at);
+int leat_sample_from_records(leat_sampler_t* handle, const leat_sample_args* args, const void* records,
+                             int32_t parts, int32_t cap, leat_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -27,6 +27,7 @@ EXPORTS = [
     "leat_sampler_tune", "leat_sampler_tune_ring", "leat_sampler_plan", "leat_sampler_last_launches",
     "leat_sampler_last_cuda_error", "leat_sample", "leat_argmax", "leat_cutoff",
     "leat_verify_draft", "leat_topk_local", "leat_sample_from_candidates", "leat_sample_static",
+    "leat_candidate_record_bytes", "leat_candidate_record_layout", "leat_sample_from_records",
 ]  # fmt: skip
 
 
@@ -78,9 +79,13 @@ def _load() -> C.CDLL:
     lib.leat_verify_draft.argtypes = [p, p, p, i32, i32, p, p, p]
     lib.leat_topk_local.argtypes = [p, C.POINTER(SampleArgs), p, p, p, p, i32, p]
     lib.leat_sample_from_candidates.argtypes = [p, C.POINTER(SampleArgs), p, p, p, p, i32, i32, p]
+    lib.leat_candidate_record_bytes.restype = sz
+    lib.leat_candidate_record_bytes.argtypes = [i32, i32]
+    lib.leat_candidate_record_layout.argtypes = [i32, i32, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]
+    lib.leat_sample_from_records.argtypes = [p, C.POINTER(SampleArgs), p, i32, i32, p]
     for name in EXPORTS:
         fn = getattr(lib, name)
-        if name not in ("leat_sampler_workspace_bytes", "leat_sampler_last_cuda_error"):
+        if name not in ("leat_sampler_workspace_bytes", "leat_sampler_last_cuda_error", "leat_candidate_record_bytes"):
             fn.restype = C.c_int
     return lib
 

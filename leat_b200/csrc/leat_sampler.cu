@@ -346,9 +346,10 @@ int leat_topk_local(leat_sampler_t* h, const leat_sample_args* a, float* cand_va
   return launch_sample(h, P, static_cast<cudaStream_t>(stream));
 }
 
-int leat_sample_from_candidates(leat_sampler_t* h, const leat_sample_args* a, const float* cand_value,
-                                const int32_t* cand_id, const int32_t* cand_count, const uint64_t* best,
-                                int32_t parts, int32_t cap, leat_stream_t stream) {
+namespace {
+int finish_from(leat_sampler* h, const leat_sample_args* a, const float* cand_value, const int32_t* cand_id,
+                const int32_t* cand_count, const uint64_t* best, long long stride_value, long long stride_id,
+                long long stride_count, long long stride_best, int32_t parts, int32_t cap, cudaStream_t stream) {
   if (!cand_value || !cand_id || !cand_count || !best || cap <= 0 || parts <= 0) return LEAT_E_ARGUMENT;
   if (!h || !a) return LEAT_E_ARGUMENT;
   // the handle is sized for this rank's slice; here `vocab` is the whole vocabulary's size
@@ -368,12 +369,55 @@ int leat_sample_from_candidates(leat_sampler_t* h, const leat_sample_args* a, co
   if (dev != h->device) return LEAT_E_DEVICE;
   P.g_value = cand_value; P.g_id = cand_id; P.g_count = cand_count;
   P.g_best = reinterpret_cast<const unsigned long long*>(best); P.g_parts = parts; P.cand_cap = cap;
+  P.g_stride_value = stride_value; P.g_stride_id = stride_id; P.g_stride_count = stride_count; P.g_stride_best = stride_best;
   const int threads = 512;
   const int shared = (int)shared_bytes(h->cap, h->keep, 0, 0);
-  finish_candidates_kernel<<<P.rows, threads, shared, static_cast<cudaStream_t>(stream)>>>(P);
+  finish_candidates_kernel<<<P.rows, threads, shared, stream>>>(P);
   if (cuda_failed(cudaGetLastError(), "finish_candidates_kernel launch")) return LEAT_E_CUDA;
   h->launches = 1;
   return LEAT_OK;
+}
+
+size_t record_offsets(int rows, int cap, size_t* id_at, size_t* count_at, size_t* best_at) {
+  const size_t values = (size_t)rows * cap * 4;
+  *id_at = values;
+  *count_at = 2 * values;
+  *best_at = (2 * values + (size_t)rows * 4 + 7) / 8 * 8;
+  return (*best_at + (size_t)rows * 8 + 255) / 256 * 256;
+}
+}  // namespace
+
+int leat_sample_from_candidates(leat_sampler_t* h, const leat_sample_args* a, const float* cand_value,
+                                const int32_t* cand_id, const int32_t* cand_count, const uint64_t* best,
+                                int32_t parts, int32_t cap, leat_stream_t stream) {
+  if (!a) return LEAT_E_ARGUMENT;
+  const long long rows = a->rows;
+  return finish_from(h, a, cand_value, cand_id, cand_count, best, rows * cap, rows * cap, rows, rows, parts, cap,
+                     static_cast<cudaStream_t>(stream));
+}
+
+size_t leat_candidate_record_bytes(int32_t rows, int32_t cap) {
+  if (rows <= 0 || cap <= 0) return 0;
+  size_t i, c, b;
+  return record_offsets(rows, cap, &i, &c, &b);
+}
+
+int leat_candidate_record_layout(int32_t rows, int32_t cap, size_t* id_at, size_t* count_at, size_t* best_at) {
+  if (rows <= 0 || cap <= 0 || !id_at || !count_at || !best_at) return LEAT_E_ARGUMENT;
+  record_offsets(rows, cap, id_at, count_at, best_at);
+  return LEAT_OK;
+}
+
+int leat_sample_from_records(leat_sampler_t* h, const leat_sample_args* a, const void* records, int32_t parts,
+                             int32_t cap, leat_stream_t stream) {
+  if (!a || !records) return LEAT_E_ARGUMENT;
+  size_t id_at, count_at, best_at;
+  const size_t bytes = record_offsets(a->rows > 0 ? a->rows : 1, cap > 0 ? cap : 1, &id_at, &count_at, &best_at);
+  const unsigned char* base = static_cast<const unsigned char*>(records);
+  return finish_from(h, a, reinterpret_cast<const float*>(base), reinterpret_cast<const int32_t*>(base + id_at),
+                     reinterpret_cast<const int32_t*>(base + count_at), reinterpret_cast<const uint64_t*>(base + best_at),
+                     (long long)(bytes / 4), (long long)(bytes / 4), (long long)(bytes / 4), (long long)(bytes / 8),
+                     parts, cap, static_cast<cudaStream_t>(stream));
 }
 
 // ---- sampling without any allocation -------------------------------------------------------------

@@ -69,6 +69,8 @@ struct KParams {
   float* cand_value; int* cand_id; int* cand_count; unsigned long long* cand_best; int cand_cap;
   // gathered candidates (finish-from-candidates kernel)
   const float* g_value; const int* g_id; const int* g_count; const unsigned long long* g_best; int g_parts;
+  // distance between two parts' arrays, in elements of each array (dense arrays or packed records)
+  long long g_stride_value, g_stride_id, g_stride_count, g_stride_best;
   // launch plan
   int slices; int slice_len; int cap; int keep; int k_max; int bm_words; int ht_size; int ring_stages;
   // workspace
@@ -1131,9 +1133,9 @@ __global__ void __launch_bounds__(512) finish_candidates_kernel(const __grid_con
   int bad = 0;
 #pragma unroll 1
   for (int j = tid; j < parts; j += nt) {
-    unsigned long long gj = P.g_best[(size_t)j * rows + b];
+    unsigned long long gj = P.g_best[(size_t)j * P.g_stride_best + b];
     g = gj > g ? gj : g;
-    if (P.g_count[(size_t)j * rows + b] < 0) bad = 1;
+    if (P.g_count[(size_t)j * P.g_stride_count + b] < 0) bad = 1;
   }
   g = warp_max_u64(g);
   if (lane == 0) atomicMax(&sm.gbest, g);
@@ -1143,8 +1145,9 @@ __global__ void __launch_bounds__(512) finish_candidates_kernel(const __grid_con
     unsigned long long a = 0ull;
 #pragma unroll 1
     for (int j = tid; j < parts; j += nt) {
-      size_t at = ((size_t)j * rows + b) * cap;
-      unsigned long long kk = make_key(P.g_value[at], (uint32_t)P.g_id[at]);
+      const size_t at = (size_t)b * cap;
+      unsigned long long kk = make_key(P.g_value[(size_t)j * P.g_stride_value + at],
+                                       (uint32_t)P.g_id[(size_t)j * P.g_stride_id + at]);
       a = kk > a ? kk : a;
     }
     a = warp_max_u64(a);
@@ -1159,9 +1162,9 @@ __global__ void __launch_bounds__(512) finish_candidates_kernel(const __grid_con
       int j = i / cap, q = i - j * cap;
       bool want = false;
       unsigned long long key = 0ull;
-      if (i < total_slots && q < P.g_count[(size_t)j * rows + b]) {
-        size_t at = ((size_t)j * rows + b) * cap + q;
-        key = make_key(P.g_value[at], (uint32_t)P.g_id[at]);
+      if (i < total_slots && q < P.g_count[(size_t)j * P.g_stride_count + b]) {
+        const size_t at = (size_t)b * cap + q;
+        key = make_key(P.g_value[(size_t)j * P.g_stride_value + at], (uint32_t)P.g_id[(size_t)j * P.g_stride_id + at]);
         want = true;
       }
       buffer_push(c, want, key);

@@ -40,15 +40,35 @@ class ShardedSampler:
             self.sampler = Sampler(max_rows, max(self.stop - self.start, 1), k_max, device)
             self.device = self.sampler.device
         d = self.device
-        # what this rank hands over, and what everybody's looks like once gathered (part-major)
-        self.count = torch.zeros(max_rows, dtype=torch.int32, device=d)
-        self.value = torch.zeros((max_rows, self.cap), dtype=torch.float32, device=d)
-        self.ids = torch.zeros((max_rows, self.cap), dtype=torch.int32, device=d)
-        self.best = torch.zeros(max_rows, dtype=torch.int64, device=d)
-        self.all_count = torch.zeros((self.world, max_rows), dtype=torch.int32, device=d)
-        self.all_value = torch.zeros((self.world, max_rows, self.cap), dtype=torch.float32, device=d)
-        self.all_ids = torch.zeros((self.world, max_rows, self.cap), dtype=torch.int32, device=d)
-        self.all_best = torch.zeros((self.world, max_rows), dtype=torch.int64, device=d)
+        # what this rank hands over is one packed record (scores, ids, counts, greedy keys), so that
+        # a single all-gather moves it; `all_records` is every rank's record, part-major
+        if self.sampler is not None:
+            size = _lib.lib.leat_candidate_record_bytes(max_rows, self.cap)
+            at = [C.c_size_t(), C.c_size_t(), C.c_size_t()]
+            _lib.check(_lib.lib.leat_candidate_record_layout(max_rows, self.cap, *(C.byref(x) for x in at)),
+                       "leat_candidate_record_layout")  # fmt: skip
+            id_at, count_at, best_at = (x.value for x in at)
+        else:  # host-side stand-ins: the same layout, computed here
+            values = max_rows * self.cap * 4
+            id_at, count_at = values, 2 * values
+            best_at = (2 * values + max_rows * 4 + 7) // 8 * 8
+            size = (best_at + max_rows * 8 + 255) // 256 * 256
+        self.record = torch.zeros(size, dtype=torch.uint8, device=d)
+        self.all_records = torch.zeros(self.world * size, dtype=torch.uint8, device=d)
+        rc = max_rows * self.cap
+
+        def views(buffer, parts):
+            per = buffer.view(parts, size)
+            value = per[:, :id_at].view(torch.float32).view(parts, max_rows, self.cap)
+            ids = per[:, id_at:count_at].view(torch.int32).view(parts, max_rows, self.cap)
+            count = per[:, count_at:count_at + max_rows * 4].view(torch.int32).view(parts, max_rows)
+            best = per[:, best_at:best_at + max_rows * 8].view(torch.int64).view(parts, max_rows)
+            return value, ids, count, best
+
+        value, ids, count, best = views(self.record, 1)
+        self.value, self.ids, self.count, self.best = value[0], ids[0], count[0], best[0]
+        self.all_value, self.all_ids, self.all_count, self.all_best = views(self.all_records, self.world)
+        del rc
 
     # ---- the three steps ----------------------------------------------------------------------
 
@@ -70,14 +90,10 @@ class ShardedSampler:
         del keep
 
     def exchange(self, rows: int) -> None:
-        """One all-gather per array: every rank ends with every rank's candidates, part-major."""
+        """One all-gather: every rank ends with every rank's record, part-major."""
         if rows != self.max_rows:
             raise ValueError("the gather buffers are sized for max_rows rows")
-        # outputs viewed as the inputs concatenated along their first axis (part-major)
-        dist.all_gather_into_tensor(self.all_count.view(-1), self.count, group=self.group)
-        dist.all_gather_into_tensor(self.all_value.view(-1, self.cap), self.value, group=self.group)
-        dist.all_gather_into_tensor(self.all_ids.view(-1, self.cap), self.ids, group=self.group)
-        dist.all_gather_into_tensor(self.all_best.view(-1), self.best, group=self.group)
+        dist.all_gather_into_tensor(self.all_records, self.record, group=self.group)
 
     def finish(self, rows, options, seed, position, uniform=None, width: int = 0, flags: int = 0,
                out: torch.Tensor | None = None) -> Sampled:  # fmt: skip
@@ -100,10 +116,9 @@ class ShardedSampler:
             result.prob_ids = torch.empty((rows, width), dtype=torch.int32, device=d)
             a.out_probs, a.out_prob_ids, a.out_width = result.probs.data_ptr(), result.prob_ids.data_ptr(), width
         with torch.cuda.device(d):
-            _lib.check(_lib.lib.leat_sample_from_candidates(
-                self.sampler.handle, C.byref(a), self.all_value.data_ptr(), self.all_ids.data_ptr(),
-                self.all_count.data_ptr(), self.all_best.data_ptr(), self.world, self.cap, _stream()),
-                "leat_sample_from_candidates")  # fmt: skip
+            _lib.check(_lib.lib.leat_sample_from_records(
+                self.sampler.handle, C.byref(a), self.all_records.data_ptr(), self.world, self.cap, _stream()),
+                "leat_sample_from_records")  # fmt: skip
         del keep
         return result
 

@@ -124,3 +124,34 @@ def test_verify_draft_accepts_and_rejects(device):
     kept, toks = oracle.verify_draft_greedy(drafted, greedy, sampled)
     np.testing.assert_array_equal(accepted.cpu().numpy(), kept)
     np.testing.assert_array_equal(tokens.cpu().numpy(), toks)
+
+
+def test_sharded_sampler_over_nccl_with_one_rank(device):
+    """The host class end to end on a real process group (one rank: the all-gather of the packed
+    records is then a copy), against the oracle."""
+    import os
+    import socket
+
+    import torch
+    import torch.distributed as dist
+
+    from leat_b200 import workloads
+    from leat_b200.sharded import ShardedSampler
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+    try:
+        w = workloads.config5(rows=16, vocab=201088)
+        sharded = ShardedSampler(w.rows, w.vocab, k_max=64, cap=128, device=device)
+        t = lambda x: torch.as_tensor(x).to(device)  # noqa: E731
+        seed = torch.as_tensor(w.seed.astype(np.int64)).to(device).to(torch.uint32)
+        got = sharded.sample(t(w.logits), t(w.options), seed, t(w.position), history=t(w.history),
+                             penalties=t(w.penalties), uniform=t(w.uniform), width=64)  # fmt: skip
+        torch.cuda.synchronize()
+        helpers.compare(helpers.oracle_run(w, "U"), got, 64, max_fragile=0)
+    finally:
+        dist.destroy_process_group()
