@@ -37,8 +37,10 @@ FALLBACK_HBM_GBS = 6650.0  # an earlier measurement on this pool, used when MEAS
 NORTH_STAR_HBM_GBS = 8000.0
 L2_BYTES = 126 << 20
 # DRAM bytes the sampling kernel moved per algorithmic byte in the ncu capture summarised in
-# profiles/sample_kernel_c3.md (dram__bytes_read.sum + dram__bytes_write.sum over B x V x 4)
-TRAFFIC_PER_ALGORITHMIC_BYTE = None
+# profiles/sample_kernel_c3_160rows.md: (dram__bytes_read.sum + dram__bytes_write.sum) / (B x V x 4)
+# = (189.6 + 14.7) MB / 167.8 MB on 160 rows of the large-batch configuration; traffic grows with
+# the rows and the vocabulary, so it is scaled to the launch being reported
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.22
 
 
 def peak_hbm() -> tuple[float, str]:
@@ -230,6 +232,26 @@ def time_graph(step, steps: int, warmup: int, inner: int) -> float:
     return a.elapsed_time(b) / (replays * inner)
 
 
+def run_one(args) -> None:
+    """One configuration, a few Python-launched steps: the command ncu captures are taken from."""
+    import torch
+
+    from leat_b200 import workloads
+    from leat_b200.sampler import Sampler
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    kw = {"rows": args.rows} if args.rows and args.workload != 4 else {}
+    w = workloads.CONFIGS[args.workload](**kw)
+    sampler = Sampler(max(w.rows, 8), w.vocab, 256, device)
+    dw = DeviceWorkload(w, device, min_pool_bytes=0, max_copies=1)
+    ms = time_device(lambda i: dw.step(sampler, i), args.steps, args.warmup)
+    print(json.dumps({"workload": WORKLOAD_NAMES[args.workload], "rows": w.rows, "vocab": w.vocab, "ms_per_step": ms,
+                      "launch": dict(zip(("threads", "slices", "shared_bytes"),
+                                         sampler.plan(w.rows, w.vocab, 0 if w.history is None else w.history.shape[1]))),
+                      "kernels_per_step": sampler.last_launches}), flush=True)
+
+
 def run_single(args) -> None:
     import torch
 
@@ -399,9 +421,14 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--workload", type=int, default=0, choices=[0, 1, 2, 3, 4, 5],
+                        help="profiling aid: time only this configuration, launched from Python, and print a short line")
+    parser.add_argument("--rows", type=int, default=0, help="with --workload: fewer rows than the configuration has")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
+    if args.workload:
+        run_one(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif int(os.environ.get("WORLD_SIZE", 1)) > 1:
         run_sharded(args)
