@@ -223,9 +223,10 @@ __device__ __forceinline__ int bucket_of(uint32_t v, float low_v, float scale, u
 // by the chosen bucket's bits.  M_SELECT_MINP: the largest score held plus log(min_p).  Every entry
 // at or above the threshold stays; sm.tau becomes the threshold.
 //
-// Raw mode: slots [0, conv) hold keys and warp w's raw (logit, index) pairs sit in
+// `raw` bit 0 (raw mode): slots [0, conv) hold keys and warp w's raw (logit, index) pairs sit in
 // [keep + w * region, ... + wcount[w]); every other slot is ignored.  Otherwise slots [0, n) hold
-// keys.  On entry the histogram is zero and vmin / vmax / m / valid are reset (kernel start and the
+// keys.  `raw` bit 1: a slice's last rebuild before it publishes: if little more than k entries are
+// live they all stay (the row's last block selects among all slices' anyway).  On entry the histogram is zero and vmin / vmax / m / valid are reset (kernel start and the
 // end of every rebuild see to that), which keeps the barriers down to five.
 __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
   Shared& sm = *c.sm;
@@ -235,7 +236,7 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
   RB_BEGIN();
   const int region = c.region;
   const int conv = sm.conv;
-  const int n = raw ? c.keep + nwarps * region : min(sm.n, c.cap);
+  const int n = (raw & 1) ? c.keep + nwarps * region : min(sm.n, c.cap);
   // ---- A: make raw pairs keys; smallest, largest and number of live keys ----
   {
     const float tau = sm.tau;
@@ -244,7 +245,7 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
 #pragma unroll 1
     for (int i = tid; i < n; i += nt) {
       unsigned long long key = 0ull;
-      if (!raw || i < conv) {
+      if (!(raw & 1) || i < conv) {
         key = buf[i];
       } else if (i >= c.keep) {
         // a history token's raw logit is dropped (the history pass gave its penalised one), and
@@ -260,7 +261,7 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
           if (!drop && sc >= tau) key = make_key(sc, (uint32_t)(idx + c.off));
         }
       }
-      if (raw) buf[i] = key;
+      if (raw & 1) buf[i] = key;
       if (key) {
         const uint32_t v = key_vbits(key);
         mx = max(mx, v);
@@ -283,7 +284,7 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
   bool by_bucket = false;
   if (live > 0 && c.mode == M_SELECT_MINP) {
     thr = ord32(unord32(hi) + c.logm + 0.0f);
-  } else if (live > c.k) {
+  } else if (live > c.k && !((raw & 2) && live <= c.k + max(8, c.k >> 3))) {
     unsigned above = 0u;           // entries above hi
     unsigned rem = (unsigned)c.k;  // the one sought is the rem-th largest within [lo, hi]
     const float top_v = unord32(hi);
@@ -996,7 +997,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   __syncthreads();
   if ((mode == M_SELECT_K || mode == M_SELECT_MINP) && !sm.overflow) {
     // the stream of a top-k row leaves raw entries behind: the rebuild also turns them into keys
-    buffer_rebuild(c, 1);
+    buffer_rebuild(c, S > 1 ? 3 : 1);
   }
   bool failed = (mode == M_GENERAL) || sm.overflow;
 
@@ -1048,22 +1049,65 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     if (lane == 0) { atomicMax(&sm.gbest, g); atomicMax(&sm.best, a); atomicMin(&sm.smin, mnb); }
     failed = __syncthreads_or(bad) != 0;
     if ((mode == M_SELECT_K || mode == M_SELECT_MINP) && !failed) {
-      const int total_slots = S * P.keep;
+      // where each slice's candidates go in the buffer: counts, then their running sum (the
+      // histogram's words are free here; they are cleared again below)
+      unsigned* counts = M.hist;
+      unsigned* starts = M.hist + S;
+      bool direct = 2 * S + 1 <= BINS;
+      if (direct) {
 #pragma unroll 1
-      for (int base = 0; base < total_slots; base += nt) {
-        int i = base + tid;
-        int j = i / P.keep, q = i - j * P.keep;
-        bool want = false;
-        unsigned long long key = 0ull;
-        if (i < total_slots && q < __ldcg(&P.ws_count[(size_t)b * S + j])) {
-          key = __ldcg(&P.ws_keys[((size_t)b * S + j) * P.keep + q]);
-          want = true;
+        for (int j = tid; j < S; j += nt) counts[j] = (unsigned)max(__ldcg(&P.ws_count[(size_t)b * S + j]), 0);
+        __syncthreads();
+        if (tid == 0) {
+          unsigned at = 0u;
+#pragma unroll 1
+          for (int j = 0; j < S; ++j) { starts[j] = at; at += counts[j]; }
+          starts[S] = at;
         }
-        buffer_push(c, want, key);
-        if (sm.overflow) break;
+        __syncthreads();
+        direct = starts[S] <= (unsigned)P.cap;
       }
-      __syncthreads();
-      if (!sm.overflow && (mode == M_SELECT_MINP || sm.n > rc.k_eff)) buffer_rebuild(c, 0);
+      if (direct) {
+        // everything fits: one gather, no barriers in between
+        const int total = (int)starts[S];
+#pragma unroll 1
+        for (int i = tid; i < total; i += nt) {
+          int lo = 0, hi = S - 1;  // the slice whose range holds i
+          while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (starts[mid] <= (unsigned)i) lo = mid; else hi = mid - 1;
+          }
+          buf[i] = __ldcg(&P.ws_keys[((size_t)b * S + lo) * P.keep + (i - (int)starts[lo])]);
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int j = tid; j < 2 * S + 1; j += nt) M.hist[j] = 0u;
+        if (tid == 0) { sm.n = total; sm.conv = total; }
+        __syncthreads();
+      } else {
+        if (2 * S + 1 <= BINS) {
+#pragma unroll 1
+          for (int j = tid; j < 2 * S + 1; j += nt) M.hist[j] = 0u;
+          __syncthreads();
+        }
+        const int total_slots = S * P.keep;
+#pragma unroll 1
+        for (int base = 0; base < total_slots; base += nt) {
+          int i = base + tid;
+          int j = i / P.keep, q = i - j * P.keep;
+          bool want = false;
+          unsigned long long key = 0ull;
+          if (i < total_slots && q < __ldcg(&P.ws_count[(size_t)b * S + j])) {
+            key = __ldcg(&P.ws_keys[((size_t)b * S + j) * P.keep + q]);
+            want = true;
+          }
+          buffer_push(c, want, key);
+          if (sm.overflow) break;
+        }
+        __syncthreads();
+      }
+      // a few hundred candidates the finish sorts as they are; more are reduced first
+      if (!sm.overflow && (mode == M_SELECT_MINP || sm.n > min(384, P.cap / 2) || P.cand_count)) buffer_rebuild(c, 0);
       failed = sm.overflow != 0;
     }
   }
