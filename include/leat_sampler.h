@@ -116,6 +116,10 @@ int leat_sampler_destroy(leat_sampler_t* handle);
 /* Launch shape override for experiments: threads per block (128, 256 or 512; 0 = automatic) and
    blocks per row (0 = automatic). */
 int leat_sampler_tune(leat_sampler_t* handle, int32_t threads, int32_t slices);
+/* The filter path (floor per row, one streaming filter, finish from the row's list) is taken for
+   16-byte aligned rows of at least 16384 tokens without a dense seen mask; 0 turns it off and every
+   row goes through the fused kernel. */
+int leat_sampler_tune_filter(leat_sampler_t* handle, int32_t enabled);
 /* Stages of the shared-memory ring the stream's bulk copies fill: 0 = automatic, 2..8 = that many,
    negative = no ring (the stream loads into registers instead). */
 int leat_sampler_tune_ring(leat_sampler_t* handle, int32_t stages);

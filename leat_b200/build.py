@@ -11,7 +11,8 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent / "csrc"
 LIBRARY = CSRC / "libleat_sampler.so"
 SOURCES = [CSRC / "leat_sampler.cu"]
-HEADERS = [CSRC / "sampler_kernels.cuh", CSRC / "device_util.cuh",
+HEADERS = [CSRC / "sampler_kernels.cuh", CSRC / "device_util.cuh", CSRC / "stream_ring.cuh",
+           CSRC / "general_kernel.cuh", CSRC / "filter_path.cuh",
            CSRC.parent.parent / "include" / "leat_sampler.h"]  # fmt: skip
 # -fmad=false: the CPU statement of the algorithm rounds every product and sum separately, and
 # ids must match it bit for bit

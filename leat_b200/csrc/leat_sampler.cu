@@ -19,6 +19,8 @@ constexpr int kMaxSliceLen = 1 << 20;  // a block may take a whole row
 constexpr int kSliceAlign = 128;
 constexpr int kMaxK = 1024;
 constexpr int kSpareCells = 4096;
+constexpr int kListCap = 4096;        // (logit, index) pairs a row's filter may list
+constexpr int kFilterMinVocab = 16384;  // narrower rows are not worth three launches
 
 thread_local char g_cuda_error[256] = "";
 
@@ -32,7 +34,7 @@ int round_up(int x, int m) { return (x + m - 1) / m * m; }
 int next_pow2(int x) { int p = 1; while (p < x) p <<= 1; return p; }
 
 struct Layout {
-  size_t keys, count, best, vmin, ticket, flag, total;
+  size_t keys, count, best, vmin, ticket, flag, list, list_count, list_floor, total;
   int cells;
 };
 
@@ -47,6 +49,9 @@ Layout layout_for(int max_rows, int max_vocab, int keep) {
   L.vmin = take((size_t)L.cells * 4);
   L.ticket = take((size_t)max_rows * 4);
   L.flag = take((size_t)max_rows * 4);
+  L.list = take((size_t)max_rows * kListCap * 8);
+  L.list_count = take((size_t)max_rows * 4);
+  L.list_floor = take((size_t)max_rows * 4);
   L.total = at;
   return L;
 }
@@ -58,7 +63,7 @@ int cap_for(int keep) { return keep <= 512 ? 2048 : 4096; }
 
 struct leat_sampler {
   int device, max_rows, max_vocab, k_max, keep, cap;
-  int tune_threads, tune_slices, tune_stages, tune_no_ring;
+  int tune_threads, tune_slices, tune_stages, tune_no_ring, tune_no_filter, has_list;
   int sm_count;
   int launches;
   unsigned char* ws;
@@ -188,6 +193,24 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
   if (!P.logits || (!P.out_ids && !P.cand_count && !P.out_cut)) return LEAT_E_ARGUMENT;
   const bool pen = P.seen != nullptr || P.history != nullptr;
   const int vec = pick_vec(P);
+  // large aligned rows take the filter path: a floor per row, one streaming filter, then one block
+  // per row finishes from the row's list
+  const bool filtered = h->has_list && !h->tune_no_filter && !P.cand_count && vec == 4 && !P.seen &&
+                        P.vocab >= kFilterMinVocab;
+  if (filtered) {
+    P.list = reinterpret_cast<unsigned long long*>(h->ws + h->L.list);
+    P.list_count = reinterpret_cast<int*>(h->ws + h->L.list_count);
+    P.list_floor = reinterpret_cast<float*>(h->ws + h->L.list_floor);
+    P.list_cap = kListCap;
+    floor_kernel<<<P.rows, SAMPLE_CHUNKS, 0, stream>>>(P);
+    if (cuda_failed(cudaGetLastError(), "floor_kernel launch")) return LEAT_E_CUDA;
+    const int per_row = (P.vocab + FILTER_SPAN - 1) / FILTER_SPAN;
+    const int items = per_row * P.rows;
+    const int blocks = items < h->sm_count * 4 ? items : h->sm_count * 4;  // four blocks fit an SM
+    filter_kernel<<<blocks, FILTER_THREADS, 0, stream>>>(P, per_row, items);
+    if (cuda_failed(cudaGetLastError(), "filter_kernel launch")) return LEAT_E_CUDA;
+    h->launches += 2;
+  }
   Plan plan = make_plan(h, P.rows, P.vocab, P.history_cap, P.history != nullptr, vec);
   P.slices = plan.slices; P.slice_len = plan.slice_len; P.bm_words = plan.bm_words; P.ht_size = plan.ht_size;
   P.ring_stages = plan.ring_stages;  // 0 unless rows are 16-byte aligned multiples of four floats
@@ -229,7 +252,7 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
   if (!h) return LEAT_E_ARGUMENT;
   h->device = device; h->max_rows = max_rows; h->max_vocab = max_vocab; h->k_max = k_max;
   h->keep = keep_for(k_max); h->cap = cap_for(h->keep);
-  h->tune_threads = 0; h->tune_slices = 0; h->tune_stages = 0; h->tune_no_ring = 0; h->launches = 0;
+  h->tune_threads = 0; h->tune_slices = 0; h->tune_stages = 0; h->tune_no_ring = 0; h->tune_no_filter = 0; h->has_list = 1; h->launches = 0;
   h->L = layout_for(max_rows, max_vocab, h->keep);
   h->ws = static_cast<unsigned char*>(workspace);
   if (bytes < h->L.total || !aligned(workspace, 256)) { delete h; return LEAT_E_WORKSPACE; }
@@ -265,6 +288,12 @@ int leat_sampler_tune(leat_sampler_t* h, int32_t threads, int32_t slices) {
   if (threads != 0 && threads != 128 && threads != 256 && threads != 512) return LEAT_E_ARGUMENT;
   if (slices < 0) return LEAT_E_ARGUMENT;
   h->tune_threads = threads; h->tune_slices = slices;
+  return LEAT_OK;
+}
+
+int leat_sampler_tune_filter(leat_sampler_t* h, int32_t enabled) {
+  if (!h) return LEAT_E_ARGUMENT;
+  h->tune_no_filter = enabled ? 0 : 1;
   return LEAT_OK;
 }
 
@@ -461,7 +490,7 @@ int static_setup(int device, StaticDevice** out) {
     leat_sampler& h = sd.handle;
     h.device = device; h.max_rows = kStaticRows; h.max_vocab = kStaticVocab; h.k_max = kStaticK;
     h.keep = keep_for(kStaticK); h.cap = cap_for(h.keep);
-    h.tune_threads = 0; h.tune_slices = 0; h.tune_stages = 0; h.tune_no_ring = 0; h.launches = 0;
+    h.tune_threads = 0; h.tune_slices = 0; h.tune_stages = 0; h.tune_no_ring = 0; h.tune_no_filter = 0; h.has_list = 0; h.launches = 0;
     Layout& L = h.L;
     L.cells = kStaticCells;
     size_t at = 0;
@@ -472,6 +501,7 @@ int static_setup(int device, StaticDevice** out) {
     L.vmin = take((size_t)L.cells * 4);
     L.ticket = take((size_t)kStaticRows * 4);
     L.flag = take((size_t)kStaticRows * 4);
+    L.list = 0; L.list_count = 0; L.list_floor = 0;  // the fixed scratch has no room for lists: the fused path is used
     L.total = at;
     if (L.total > kStaticBytes || h.keep != kStaticKeep) return LEAT_E_WORKSPACE;
     h.ws = static_cast<unsigned char*>(scratch);

@@ -80,6 +80,8 @@ struct KParams {
   float* ws_min;                // (rows, slices): smallest score of the slice
   unsigned* ws_ticket;          // (rows)
   int* ws_flag;                 // (rows): 1 = the row needs the multi-pass kernel
+  // the filter path: per row a floor, and the list of (logit, index) pairs at or above it
+  unsigned long long* list; int* list_count; float* list_floor; int list_cap;
 };
 
 struct RowCfg {
@@ -101,7 +103,8 @@ struct Shared {
   unsigned long long best;   // block max of an argmax key
   unsigned long long gbest;  // block max of the greedy key
   unsigned smin;             // block min of score bits (ord32)
-  int jstar, ns, pick;
+  int jstar, ns, pick, nstrict;
+  float floor_l, s_floor;  // the filter's floor of a listed row (+inf otherwise) and its score
   int wcount[32];  // raw entries each warp holds in its own region of the buffer
   // the block's best so far, as order-preserving bits: what a logit must reach to be looked at
   unsigned share_greedy, share_gumbel, share_min;
@@ -485,14 +488,15 @@ __device__ inline void finish_simple(const KParams& P, int b, int mode, unsigned
 // buf[0..sm.n) holds the row's candidates (unsorted).  Computes the cut and the draw and writes the
 // row's outputs.  fw / fi / fs are float scratch of cap, cap and cap/32 entries.
 __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, unsigned long long* buf,
-                                  Shared& sm, float* fw, float* fi, float* fs, float row_min) {
+                                  Shared& sm, float* fw, float* fi, float* fs, float row_min,
+                                  bool listed = false, float s_floor = 0.0f) {
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
   const int n = sm.n;
   if (n <= 0) {  // nothing comparable in the row (all NaN)
     finish_simple(P, b, rc.mode, 0ull, 0ull, true);
     return;
   }
-  if (tid == 0) { sm.jstar = 0; sm.ns = 0; sm.pick = NO_ID; sm.best = 0ull; }
+  if (tid == 0) { sm.jstar = 0; sm.ns = 0; sm.pick = NO_ID; sm.best = 0ull; sm.nstrict = 0; }
   if (n <= P.cap / 2) {
     // few candidates: a key's place is the number of keys above it (keys are distinct), one
     // sweep over shared memory and no barriers, into the buffer's upper half
@@ -562,6 +566,7 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
   for (int j = tid; j < n; j += nt) {
     float r = key_value(buf[j]);
     if (r >= cut && (j + 1 == n || !(key_value(buf[j + 1]) >= cut))) sm.ns = j + 1;
+    if (listed && r > s_floor && (j + 1 == n || !(key_value(buf[j + 1]) > s_floor))) sm.nstrict = j + 1;
   }
   __syncthreads();
   const int ns = max(sm.ns, 1);
@@ -588,6 +593,16 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
     int id;
     if (P.uniform) id = key_id(buf[min(sm.pick, ns - 1)]);
     else id = key_id(sm.best);
+    if (listed) {
+      // the list stands only if nothing the filter dropped could have mattered: enough candidates
+      // strictly above the floor's score, and the cut strictly above it
+      const bool enough = rc.mode == M_SELECT_MINP || sm.nstrict >= rc.k_eff;
+      if (!(enough && cut > s_floor)) {
+        id = -1;
+        if (!(P.flags & 2u)) P.ws_flag[b] = 1;
+        else if (P.status) atomicOr(P.status, 4);
+      }
+    }
     if (P.out_ids) P.out_ids[b] = id;
     if (P.out_cut) P.out_cut[b] = cut;
     if (P.out_kept) P.out_kept[b] = sm.ns;
@@ -644,6 +659,8 @@ struct Tracked {
 };
 
 #include "stream_ring.cuh"
+
+#include "filter_path.cuh"
 
 // The first `cap` scores of a top-k / min-p slice go straight into the candidate buffer (exact,
 // penalties applied); one rebuild gives the first threshold.  Returns where the stream starts.
@@ -885,10 +902,11 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   ring.stages = P.ring_stages;
 
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
-  const int b = blockIdx.y, slice = blockIdx.x, S = P.slices;
+  const int b = blockIdx.y, slice = blockIdx.x;
+  int S = P.slices;
   PHASE_BEGIN();
   const int begin = slice * P.slice_len;
-  const int end = min(P.vocab, begin + P.slice_len);
+  int end = min(P.vocab, begin + P.slice_len);
   const float* row = P.logits + (size_t)b * P.row_stride;
   const uint8_t* seen_row = (PEN && P.seen) ? P.seen + (size_t)b * P.seen_stride : nullptr;
   // the row's options and the buffer's description live in shared memory, not in registers
@@ -909,6 +927,13 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     sm.smin = 0xFFFFFFFFu; sm.is_last = (S == 1);
     sm.share_greedy = 0u; sm.share_gumbel = 0u; sm.share_min = 0xFFFFFFFFu;
     h.raw = hraw; h.keys = hkeys; h.counts = hcnt; h.mask = P.ht_size - 1; h.begin = begin;
+    sm.floor_l = P.list ? P.list_floor[b] : __uint_as_float(0x7F800000u);
+    sm.s_floor = neg_inf();
+    if (sm.floor_l < __uint_as_float(0x7F800000u)) {
+      // nothing scoring under the floor can matter to a row whose list stands
+      sm.s_floor = scaled(sm.floor_l, rc) + 0.0f;
+      sm.tau = sm.s_floor;
+    }
   }
   // (the other threads clear the tables meanwhile)
 #pragma unroll 1
@@ -919,6 +944,13 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   }
   __syncthreads();
   const int mode = rc.mode;
+  // a row whose logits the filter listed needs one block, which owns the whole row
+  const bool listed = sm.floor_l < __uint_as_float(0x7F800000u);
+  if (listed) {
+    if (slice > 0) return;
+    S = 1;
+    end = P.vocab;
+  }
   if (PEN && P.history) {
     // the slice's history tokens: a hash table of counts, and each token's logit fetched now (one
     // scattered load each, issued in batches) so the later passes never wait on them
@@ -960,7 +992,14 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   Tracked t;
   t.gl = neg_inf(); t.gid = NO_ID; t.al = neg_inf(); t.aid = NO_ID;
   t.mnl = __uint_as_float(0x7F800000u); t.mns = t.mnl;
-  if (mode != M_GENERAL) {
+  bool list_ok = true;
+  if (listed) {
+    // the filter already streamed the row: candidates come from its list and from the history
+    list_ok = list_load<PEN>(P, rc, c, h, b, t);
+    PHASE_MARK(1);
+    if (PEN && P.history && list_ok) slice_history<PEN>(P, rc, c, h, row, seen_row, begin, end, t);
+    PHASE_MARK(2);
+  } else if (mode != M_GENERAL) {
     const bool select = mode == M_SELECT_K || mode == M_SELECT_MINP;
     int from = begin;
     if (select) from = slice_fill<PEN>(P, rc, c, h, row, seen_row, begin, end, t);
@@ -996,10 +1035,18 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   }
   __syncthreads();
   if ((mode == M_SELECT_K || mode == M_SELECT_MINP) && !sm.overflow) {
-    // the stream of a top-k row leaves raw entries behind: the rebuild also turns them into keys
-    buffer_rebuild(c, S > 1 ? 3 : 1);
+    if (listed) {
+      // keys already; a few hundred the finish sorts as they are, more are reduced first
+      if (mode == M_SELECT_MINP || sm.n > min(384, P.cap / 2)) buffer_rebuild(c, 0);
+    } else {
+      // the stream of a top-k row leaves raw entries behind: the rebuild also turns them into keys
+      buffer_rebuild(c, S > 1 ? 3 : 1);
+    }
   }
-  bool failed = (mode == M_GENERAL) || sm.overflow;
+  bool failed = (mode == M_GENERAL) || sm.overflow || !list_ok;
+  const float floor_l = listed ? sm.floor_l : neg_inf();
+  // a greedy token is only known if the best candidate reaches the floor (nothing dropped beats it)
+  if (listed && rc.track && !(sm.gbest != 0ull && key_value(sm.gbest) >= floor_l)) failed = true;
 
   PHASE_MARK(4);
   // ---- publish, and let the last block of the row go on ----
@@ -1144,7 +1191,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     finish_simple(P, b, mode, sm.best, sm.gbest, failed);
     return;
   }
-  finish_row(P, rc, b, buf, sm, fw, fi, fs, unord32(sm.smin));
+  finish_row(P, rc, b, buf, sm, fw, fi, fs, listed ? neg_inf() : unord32(sm.smin), listed, sm.s_floor);
   PHASE_MARK(7);
 }
 

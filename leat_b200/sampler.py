@@ -97,6 +97,9 @@ class Sampler:
     def tune(self, threads: int = 0, slices: int = 0) -> None:
         _lib.check(_lib.lib.leat_sampler_tune(self.handle, threads, slices), "leat_sampler_tune")
 
+    def tune_filter(self, enabled: bool = True) -> None:
+        _lib.check(_lib.lib.leat_sampler_tune_filter(self.handle, int(enabled)), "leat_sampler_tune_filter")
+
     def tune_ring(self, stages: int = 0) -> None:
         _lib.check(_lib.lib.leat_sampler_tune_ring(self.handle, stages), "leat_sampler_tune_ring")
 
