@@ -46,6 +46,7 @@ __device__ __forceinline__ int floor_order(int k, int vocab) {
 __global__ void __launch_bounds__(SAMPLE_CHUNKS) floor_kernel(const __grid_constant__ KParams P) {
   __shared__ float maxima[SAMPLE_CHUNKS];
   __shared__ float sorted[SAMPLE_CHUNKS];
+  __shared__ RowCfg rc;
   const int b = blockIdx.x, tid = threadIdx.x;
   const float* row = P.logits + (size_t)b * P.row_stride;
   const int V = P.vocab;
@@ -56,6 +57,7 @@ __global__ void __launch_bounds__(SAMPLE_CHUNKS) floor_kernel(const __grid_const
     float4 x[SAMPLE_CHUNK / 4];
 #pragma unroll
     for (int u = 0; u < SAMPLE_CHUNK / 4; ++u) x[u] = __ldg(src + u);
+    if (tid == SAMPLE_CHUNKS - 1) rc = row_config(P, b);  // while the sample is on its way
     float m = neg_inf();  // fmaxf drops NaNs
 #pragma unroll
     for (int u = 0; u < SAMPLE_CHUNK / 4; ++u) m = fmaxf(fmaxf(m, fmaxf(x[u].x, x[u].y)), fmaxf(x[u].z, x[u].w));
@@ -75,7 +77,6 @@ __global__ void __launch_bounds__(SAMPLE_CHUNKS) floor_kernel(const __grid_const
   }
   __syncthreads();
   if (tid == 0) {
-    const RowCfg rc = row_config(P, b);
     const int mode = rc.mode;
     float floor_l = pos_inf();  // nothing is listed
     if (mode == M_SELECT_K) {
@@ -182,8 +183,8 @@ __global__ void __launch_bounds__(FILTER_THREADS, 4) filter_kernel(const __grid_
 }
 
 // sample_kernel's replacement for the stream on a row that has a list: the listed logits become
-// (score, id) keys in the candidate buffer (history tokens are skipped: the history pass gives
-// their penalised scores), and the greedy best among them is tracked.  False if the list ran over.
+// (score, id) keys in the candidate buffer, history tokens among them penalised, and the greedy
+// best among them is tracked.  False if the list ran over.
 template <bool PEN>
 __device__ __noinline__ bool list_load(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
                                        int b, Tracked& t) {
@@ -200,10 +201,18 @@ __device__ __noinline__ bool list_load(const KParams& P, const RowCfg& rc, const
     unsigned long long key = 0ull;
     if (i < listed) {
       const unsigned long long pair = __ldcg(&list[i]);
-      const float l = __uint_as_float((uint32_t)(pair >> 32));
       const int idx = (int)(uint32_t)pair;
+      float l = __uint_as_float((uint32_t)(pair >> 32));
       bool skip = false;
-      if (PEN && P.history) skip = in_history(h.keys, h.mask, idx);
+      if (PEN && P.history) {
+        // a history token: penalised here if penalties only lower logits (then those that matter are
+        // all listed), else left to the history pass, which fetches every history token's logit
+        const int count = history_count(h, idx);
+        if (count) {
+          if (rc.lowers) l = penalised(l, count, rc);
+          else skip = true;
+        }
+      }
       if (!skip) {
         if (rc.track && (l > t.gl || (l == t.gl && idx < t.gid))) { t.gl = l; t.gid = idx; }
         const float s = scaled(l, rc);

@@ -87,6 +87,7 @@ struct KParams {
 struct RowCfg {
   float T, k, p, m, rinv, tf, rep, pres, freq, u, logm;
   int mode, k_eff, has_cut, greedy, track, divide;
+  int lowers;  // the penalties can only lower a logit (repetition >= 1, presence and frequency >= 0)
   uint32_t rkey;
 };
 
@@ -171,6 +172,7 @@ __device__ inline RowCfg row_config(const KParams& P, int b) {
     const float* q = P.penalties + (size_t)(P.penalties_rows == 1 ? 0 : b) * 3;
     rc.rep = q[0]; rc.pres = q[1]; rc.freq = q[2];
   }
+  rc.lowers = (rc.rep >= 1.0f && rc.pres >= 0.0f && rc.freq >= 0.0f) ? 1 : 0;
   rc.tf = fmaxf(rc.T, 1e-6f);
   rc.rinv = 1.0f / rc.tf;
   rc.divide = (P.flags & 1u) ? 1 : 0;
@@ -956,6 +958,9 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     // scattered load each, issued in batches) so the later passes never wait on them
     const int hl = P.history_len ? min(P.history_len[b], P.history_cap) : P.history_cap;
     const int* hist_ids = P.history + (size_t)b * P.history_cap;
+    // a listed row whose penalties only lower logits finds every history token that matters in its
+    // list, logit included: nothing to fetch
+    const bool fetch = !(listed && rc.lowers);
     constexpr int IB = 4;
 #pragma unroll 1
     for (int base = 0; base < hl; base += nt * IB) {
@@ -969,7 +974,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
         ids[j] = id;
       }
 #pragma unroll
-      for (int j = 0; j < IB; ++j) raw[j] = ids[j] >= 0 ? row[ids[j]] : 0.0f;
+      for (int j = 0; j < IB; ++j) raw[j] = (fetch && ids[j] >= 0) ? row[ids[j]] : 0.0f;
 #pragma unroll
       for (int j = 0; j < IB; ++j) {
         const int id = ids[j];
@@ -997,7 +1002,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     // the filter already streamed the row: candidates come from its list and from the history
     list_ok = list_load<PEN>(P, rc, c, h, b, t);
     PHASE_MARK(1);
-    if (PEN && P.history && list_ok) slice_history<PEN>(P, rc, c, h, row, seen_row, begin, end, t);
+    if (PEN && P.history && list_ok && !rc.lowers) slice_history<PEN>(P, rc, c, h, row, seen_row, begin, end, t);
     PHASE_MARK(2);
   } else if (mode != M_GENERAL) {
     const bool select = mode == M_SELECT_K || mode == M_SELECT_MINP;
