@@ -57,7 +57,11 @@ __global__ void __launch_bounds__(SAMPLE_CHUNKS) floor_kernel(const __grid_const
     float4 x[SAMPLE_CHUNK / 4];
 #pragma unroll
     for (int u = 0; u < SAMPLE_CHUNK / 4; ++u) x[u] = __ldg(src + u);
-    if (tid == SAMPLE_CHUNKS - 1) rc = row_config(P, b);  // while the sample is on its way
+    if (tid >= SAMPLE_CHUNKS - 32) {  // the last warp fetches the row's options while the sample is on its way
+      uint32_t unused;
+      const RowIn in = row_inputs_warp(P, b, nullptr, unused);
+      if (tid == SAMPLE_CHUNKS - 1) rc = row_config_from(P, in);
+    }
     float m = neg_inf();  // fmaxf drops NaNs
 #pragma unroll
     for (int u = 0; u < SAMPLE_CHUNK / 4; ++u) m = fmaxf(fmaxf(m, fmaxf(x[u].x, x[u].y)), fmaxf(x[u].z, x[u].w));
@@ -184,13 +188,13 @@ __global__ void __launch_bounds__(FILTER_THREADS, 4) filter_kernel(const __grid_
 
 // sample_kernel's replacement for the stream on a row that has a list: the listed logits become
 // (score, id) keys in the candidate buffer, history tokens among them penalised, and the greedy
-// best among them is tracked.  False if the list ran over.
+// best among them is tracked.  `listed` is the list's length and first_pair this thread's entry of
+// the first round, both loaded by the caller ahead of time.  False if the list ran over.
 template <bool PEN>
 __device__ __noinline__ bool list_load(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
-                                       int b, Tracked& t) {
+                                       int b, Tracked& t, int listed, unsigned long long first_pair) {
   Shared& sm = *c.sm;
   const int tid = threadIdx.x, nt = blockDim.x;
-  const int listed = __ldcg(&P.list_count[b]);
   if (listed > P.list_cap) return false;
   const unsigned long long* list = P.list + (size_t)b * P.list_cap;
   const bool select = rc.mode == M_SELECT_K || rc.mode == M_SELECT_MINP;
@@ -200,7 +204,7 @@ __device__ __noinline__ bool list_load(const KParams& P, const RowCfg& rc, const
     bool want = false;
     unsigned long long key = 0ull;
     if (i < listed) {
-      const unsigned long long pair = __ldcg(&list[i]);
+      const unsigned long long pair = base == 0 ? first_pair : __ldcg(&list[i]);
       const int idx = (int)(uint32_t)pair;
       float l = __uint_as_float((uint32_t)(pair >> 32));
       bool skip = false;

@@ -27,6 +27,8 @@ __device__ unsigned long long g_phase_cycles[32];
 #define RB_MARK(i) do { if (threadIdx.x == 0) { long long now_ = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(now_ - rb_t0_)); rb_t0_ = now_; } } while (0)
 #define RB_BEGIN() long long rb_t0_ = clock64()
 #define RB_ADD1(i) atomicAdd(&g_phase_cycles[i], 1ull)
+#define FIN_MARK(i) do { __syncthreads(); RB_MARK(i); } while (0)
+#define SETUP_MARK(i) do { if (threadIdx.x == 0) atomicAdd(&g_phase_cycles[i], (unsigned long long)(clock64() - phase_t0_)); } while (0)
 #define PHASE_MARK(i) do { __syncthreads(); if (threadIdx.x == 0) { long long now_ = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(now_ - phase_t0_)); phase_t0_ = now_; } } while (0)
 #define PHASE_BEGIN() long long phase_t0_ = clock64()
 #else
@@ -35,6 +37,8 @@ __device__ unsigned long long g_phase_cycles[32];
 #define RB_MARK(i) do { } while (0)
 #define RB_BEGIN() do { } while (0)
 #define RB_ADD1(i) do { } while (0)
+#define FIN_MARK(i) do { } while (0)
+#define SETUP_MARK(i) do { } while (0)
 #endif
 
 enum RowMode : int {
@@ -157,34 +161,92 @@ __device__ __forceinline__ float logit_floor(float tau, float tf) {
   return g - fabsf(g) * 9.5367431640625e-07f - 1e-37f;
 }
 
-__device__ inline RowCfg row_config(const KParams& P, int b) {
-  RowCfg rc;
+// a row's raw inputs, before anything is derived from them
+struct RowIn {
+  float T, k, p, m, pres, rep, freq, u;
+  uint32_t seed;
+  int pos;
+};
+
+__device__ inline RowIn row_inputs(const KParams& P, int b) {
+  RowIn in;
   if (P.options) {
     const float* o = P.options + (size_t)(P.options_rows == 1 ? 0 : b) * 5;
-    rc.T = o[0]; rc.k = o[1]; rc.p = o[2]; rc.m = o[3]; rc.pres = o[4];
+    in.T = o[0]; in.k = o[1]; in.p = o[2]; in.m = o[3]; in.pres = o[4];
   } else if (P.opt_k) {
-    rc.T = 1.0f; rc.k = P.opt_k[b]; rc.p = P.opt_p[b]; rc.m = P.opt_m[b]; rc.pres = 0.0f;
+    in.T = 1.0f; in.k = P.opt_k[b]; in.p = P.opt_p[b]; in.m = P.opt_m[b]; in.pres = 0.0f;
   } else {
-    rc.T = 0.0f; rc.k = 0.0f; rc.p = 1.0f; rc.m = 0.0f; rc.pres = 0.0f;
+    in.T = 0.0f; in.k = 0.0f; in.p = 1.0f; in.m = 0.0f; in.pres = 0.0f;
   }
-  rc.rep = 1.0f; rc.freq = 0.0f;
+  in.rep = 1.0f; in.freq = 0.0f;
   if (P.penalties) {
     const float* q = P.penalties + (size_t)(P.penalties_rows == 1 ? 0 : b) * 3;
-    rc.rep = q[0]; rc.pres = q[1]; rc.freq = q[2];
+    in.rep = q[0]; in.pres = q[1]; in.freq = q[2];
   }
+  in.u = P.uniform ? P.uniform[b] : 0.0f;
+  in.seed = P.seed ? P.seed[P.seed_rows == 1 ? 0 : b] : 0u;
+  in.pos = P.position ? P.position[P.position_rows == 1 ? 0 : b] : 0;
+  return in;
+}
+
+// The same inputs, fetched by a whole warp at once: every word comes from a lane of its own, so
+// the loads overlap instead of following one another.  `extra` (may be null) is one more word to
+// fetch alongside; it comes back in extra_out.
+__device__ inline RowIn row_inputs_warp(const KParams& P, int b, const void* extra, uint32_t& extra_out) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t* src = nullptr;
+  if (lane < 5) {
+    if (P.options) src = reinterpret_cast<const uint32_t*>(P.options + (size_t)(P.options_rows == 1 ? 0 : b) * 5 + lane);
+    else if (P.opt_k && lane == 1) src = reinterpret_cast<const uint32_t*>(P.opt_k + b);
+    else if (P.opt_k && lane == 2) src = reinterpret_cast<const uint32_t*>(P.opt_p + b);
+    else if (P.opt_k && lane == 3) src = reinterpret_cast<const uint32_t*>(P.opt_m + b);
+  } else if (lane < 8) {
+    if (P.penalties) src = reinterpret_cast<const uint32_t*>(P.penalties + (size_t)(P.penalties_rows == 1 ? 0 : b) * 3 + (lane - 5));
+  } else if (lane == 8) {
+    if (P.uniform) src = reinterpret_cast<const uint32_t*>(P.uniform + b);
+  } else if (lane == 9) {
+    if (P.seed) src = P.seed + (P.seed_rows == 1 ? 0 : b);
+  } else if (lane == 10) {
+    if (P.position) src = reinterpret_cast<const uint32_t*>(P.position + (P.position_rows == 1 ? 0 : b));
+  } else if (lane == 11) {
+    src = reinterpret_cast<const uint32_t*>(extra);
+  }
+  const uint32_t w = src ? *src : 0u;
+  uint32_t v[12];
+#pragma unroll
+  for (int i = 0; i < 12; ++i) v[i] = __shfl_sync(FULL, w, i);
+  RowIn in;
+  if (P.options) {
+    in.T = __uint_as_float(v[0]); in.k = __uint_as_float(v[1]); in.p = __uint_as_float(v[2]);
+    in.m = __uint_as_float(v[3]); in.pres = __uint_as_float(v[4]);
+  } else if (P.opt_k) {
+    in.T = 1.0f; in.k = __uint_as_float(v[1]); in.p = __uint_as_float(v[2]); in.m = __uint_as_float(v[3]); in.pres = 0.0f;
+  } else {
+    in.T = 0.0f; in.k = 0.0f; in.p = 1.0f; in.m = 0.0f; in.pres = 0.0f;
+  }
+  in.rep = 1.0f; in.freq = 0.0f;
+  if (P.penalties) { in.rep = __uint_as_float(v[5]); in.pres = __uint_as_float(v[6]); in.freq = __uint_as_float(v[7]); }
+  in.u = __uint_as_float(v[8]);
+  in.seed = v[9];
+  in.pos = (int)v[10];
+  extra_out = v[11];
+  return in;
+}
+
+__device__ inline RowCfg row_config_from(const KParams& P, const RowIn& in) {
+  RowCfg rc;
+  rc.T = in.T; rc.k = in.k; rc.p = in.p; rc.m = in.m; rc.pres = in.pres; rc.rep = in.rep; rc.freq = in.freq;
   rc.lowers = (rc.rep >= 1.0f && rc.pres >= 0.0f && rc.freq >= 0.0f) ? 1 : 0;
   rc.tf = fmaxf(rc.T, 1e-6f);
   rc.rinv = 1.0f / rc.tf;
   rc.divide = (P.flags & 1u) ? 1 : 0;
-  rc.u = P.uniform ? P.uniform[b] : 0.0f;
+  rc.u = in.u;
   rc.logm = log_ref(rc.m);
   rc.greedy = (P.force_greedy || !(rc.T > 0.0f)) ? 1 : 0;
   rc.has_cut = (rc.k > 0.0f || rc.p < 1.0f || rc.m > 0.0f) ? 1 : 0;
   int V = P.vocab;
   rc.k_eff = (rc.k > 0.0f) ? max(1, (int)fminf(floorf(rc.k), (float)V)) : V;
-  uint32_t seed = P.seed ? P.seed[P.seed_rows == 1 ? 0 : b] : 0u;
-  int pos = P.position ? P.position[P.position_rows == 1 ? 0 : b] : 0;
-  rc.rkey = row_key(seed, pos);
+  rc.rkey = row_key(in.seed, in.pos);
   int vt = P.vocab_total > 0 ? P.vocab_total : V;
   if (rc.greedy) rc.mode = M_ARGMAX_L;
   else if (!rc.has_cut && !P.uniform && vt > P.k_max) rc.mode = M_ARGMAX_G;
@@ -194,6 +256,8 @@ __device__ inline RowCfg row_config(const KParams& P, int b) {
   rc.track = (P.out_greedy != nullptr || P.cand_best != nullptr || rc.mode == M_ARGMAX_L) ? 1 : 0;
   return rc;
 }
+
+__device__ inline RowCfg row_config(const KParams& P, int b) { return row_config_from(P, row_inputs(P, b)); }
 
 // ---- candidate buffer -------------------------------------------------------------------------
 
@@ -494,14 +558,49 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
                                   bool listed = false, float s_floor = 0.0f) {
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
   const int n = sm.n;
+  RB_BEGIN();
   if (n <= 0) {  // nothing comparable in the row (all NaN)
     finish_simple(P, b, rc.mode, 0ull, 0ull, true);
     return;
   }
   if (tid == 0) { sm.jstar = 0; sm.ns = 0; sm.pick = NO_ID; sm.best = 0ull; sm.nstrict = 0; }
-  if (n <= P.cap / 2) {
-    // few candidates: a key's place is the number of keys above it (keys are distinct), one
-    // sweep over shared memory and no barriers, into the buffer's upper half
+  if (n <= nt) {
+    // one key per thread: every warp sorts its 32 keys in registers, then a key's place is its place
+    // in its own run plus, for every other run, the number of keys there above it (a binary search)
+    unsigned long long* runs = buf + P.cap / 2;
+    unsigned long long key = tid < n ? buf[tid] : 0ull;
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+      for (int j = k >> 1; j > 0; j >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(FULL, key, j);
+        const bool keep_max = ((lane & k) == 0) == ((lane & j) == 0);
+        const unsigned long long hi = key > other ? key : other, lo = key > other ? other : key;
+        key = keep_max ? hi : lo;
+      }
+    }
+    const int nruns = (n + 31) >> 5;
+    if (warp < nruns) runs[tid] = key;
+    __syncthreads();
+    if (key != 0ull) {
+      int place = lane;
+#pragma unroll 2
+      for (int r = 0; r < nruns; ++r) {
+        if (r == warp) continue;
+        const unsigned long long* a = runs + r * 32;
+        int pos = 0;
+#pragma unroll
+        for (int step = 16; step > 0; step >>= 1)
+          if (a[pos + step - 1] > key) pos += step;
+        if (pos == 31 && a[31] > key) pos = 32;
+        place += pos;
+      }
+      buf[place] = key;  // every key is in registers or in `runs` by now: the front is free
+    }
+    __syncthreads();
+  } else if (n <= P.cap / 2) {
+    // a key's place is the number of keys above it (keys are distinct), one sweep over shared
+    // memory and no barriers, into the buffer's upper half
     unsigned long long* sorted = buf + P.cap / 2;
 #pragma unroll 1
     for (int i = tid; i < n; i += nt) {
@@ -525,6 +624,7 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
     __syncthreads();
     block_sort_desc(buf, p2);
   }
+  FIN_MARK(25);
   const float top = key_value(buf[0]);
   const int in_k = min(rc.k_eff, n);
   const int nseg = (n + 31) >> 5;
@@ -552,14 +652,22 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
 #pragma unroll 1
   for (int j = tid; j < n; j += nt) fi[j] = fs[j >> 5] + fi[j];
   __syncthreads();
+  FIN_MARK(26);
   const float kept = fi[in_k - 1];
   const float bound_p = rc.p * kept;
+  {
+    // the last place whose likelier mass stays under the bound: one shared atomic per warp
+    int last = 0;
 #pragma unroll 1
-  for (int j = tid; j < in_k; j += nt) {
-    float likelier = fi[j] - fw[j];
-    if (j == 0 || likelier < bound_p) atomicMax(&sm.jstar, j);
+    for (int j = tid; j < in_k; j += nt) {
+      float likelier = fi[j] - fw[j];
+      if (j == 0 || likelier < bound_p) last = j;
+    }
+    last = __reduce_max_sync(FULL, last);
+    if (lane == 0 && last > 0) atomicMax(&sm.jstar, last);
   }
   __syncthreads();
+  FIN_MARK(27);
   float base = (rc.p < 1.0f) ? key_value(buf[sm.jstar]) : key_value(buf[in_k - 1]);
   if (rc.mode == M_SELECT_MINP) base = row_min;  // k = 0: the k-th score is the row's last
   float cut = fmaxf(base, top + rc.logm);
@@ -571,13 +679,17 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
     if (listed && r > s_floor && (j + 1 == n || !(key_value(buf[j + 1]) > s_floor))) sm.nstrict = j + 1;
   }
   __syncthreads();
+  FIN_MARK(28);
   const int ns = max(sm.ns, 1);
   const float total = fi[ns - 1];
   if (P.uniform) {
     const float bound_u = rc.u * total;
+    int first = NO_ID;
 #pragma unroll 1
     for (int j = tid; j < ns; j += nt)
-      if (fi[j] > bound_u) atomicMin(&sm.pick, j);
+      if (fi[j] > bound_u) first = min(first, j);
+    first = __reduce_min_sync(FULL, first);
+    if (lane == 0 && first != NO_ID) atomicMin(&sm.pick, first);
   } else {
     unsigned long long best = 0ull;
 #pragma unroll 1
@@ -591,6 +703,7 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
     if (lane == 0) atomicMax(&sm.best, best);
   }
   __syncthreads();
+  FIN_MARK(29);
   if (tid == 0) {
     int id;
     if (P.uniform) id = key_id(buf[min(sm.pick, ns - 1)]);
@@ -912,12 +1025,34 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   const float* row = P.logits + (size_t)b * P.row_stride;
   const uint8_t* seen_row = (PEN && P.seen) ? P.seen + (size_t)b * P.seen_stride : nullptr;
   // the row's options and the buffer's description live in shared memory, not in registers
+  // loads nothing else depends on go out first: the first history ids, the list's length and entry
+  constexpr int IB = 4;
+  const int* hist_ids = (PEN && P.history) ? P.history + (size_t)b * P.history_cap : nullptr;
+  int pre_ids[IB];
+  int pre_hl = 0;
+  if (PEN && P.history) {
+#pragma unroll
+    for (int j = 0; j < IB; ++j) {
+      const int i = j * nt + tid;
+      pre_ids[j] = i < P.history_cap ? hist_ids[i] : -1;
+    }
+    pre_hl = P.history_len ? P.history_len[b] : P.history_cap;
+  }
+  int pre_count = 0;
+  unsigned long long pre_pair = 0ull;
+  if (P.list && slice == 0) {
+    pre_count = __ldcg(&P.list_count[b]);
+    pre_pair = __ldcg(&P.list[(size_t)b * P.list_cap + tid]);
+  }
   RowCfg& rc = *M.rc;
   Ctx& c = *M.ctx;
   History& h = *M.history;  // in shared memory: the out-of-line stream functions take it by reference
   float* hraw = reinterpret_cast<float*>(hcnt + P.ht_size);
+  RowIn in;
+  uint32_t floor_bits = 0x7F800000u;
+  if (tid < 32) in = row_inputs_warp(P, b, P.list ? P.list_floor + b : nullptr, floor_bits);
   if (tid == 0) {
-    rc = row_config(P, b);
+    rc = row_config_from(P, in);
     c.buf = buf; c.stage = M.stage; c.hist = M.hist; c.sm = M.sm;
     c.cap = P.cap; c.keep = P.keep; c.mode = rc.mode; c.k = rc.k_eff; c.logm = rc.logm;
     c.divide = rc.divide; c.off = P.vocab_offset; c.begin = begin; c.rinv = rc.rinv; c.tf = rc.tf;
@@ -929,7 +1064,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     sm.smin = 0xFFFFFFFFu; sm.is_last = (S == 1);
     sm.share_greedy = 0u; sm.share_gumbel = 0u; sm.share_min = 0xFFFFFFFFu;
     h.raw = hraw; h.keys = hkeys; h.counts = hcnt; h.mask = P.ht_size - 1; h.begin = begin;
-    sm.floor_l = P.list ? P.list_floor[b] : __uint_as_float(0x7F800000u);
+    sm.floor_l = P.list ? __uint_as_float(floor_bits) : __uint_as_float(0x7F800000u);
     sm.s_floor = neg_inf();
     if (sm.floor_l < __uint_as_float(0x7F800000u)) {
       // nothing scoring under the floor can matter to a row whose list stands
@@ -945,6 +1080,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     for (int i = tid; i < P.ht_size; i += nt) { hkeys[i] = HASH_EMPTY; hcnt[i] = 0; }
   }
   __syncthreads();
+  SETUP_MARK(8);
   const int mode = rc.mode;
   // a row whose logits the filter listed needs one block, which owns the whole row
   const bool listed = sm.floor_l < __uint_as_float(0x7F800000u);
@@ -956,12 +1092,10 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   if (PEN && P.history) {
     // the slice's history tokens: a hash table of counts, and each token's logit fetched now (one
     // scattered load each, issued in batches) so the later passes never wait on them
-    const int hl = P.history_len ? min(P.history_len[b], P.history_cap) : P.history_cap;
-    const int* hist_ids = P.history + (size_t)b * P.history_cap;
+    const int hl = min(pre_hl, P.history_cap);
     // a listed row whose penalties only lower logits finds every history token that matters in its
     // list, logit included: nothing to fetch
     const bool fetch = !(listed && rc.lowers);
-    constexpr int IB = 4;
 #pragma unroll 1
     for (int base = 0; base < hl; base += nt * IB) {
       int ids[IB];
@@ -969,9 +1103,16 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
 #pragma unroll
       for (int j = 0; j < IB; ++j) {
         const int i = base + j * nt + tid;
-        int id = i < hl ? hist_ids[i] - P.vocab_offset : -1;
+        int id = i < hl ? pre_ids[j] - P.vocab_offset : -1;
         if (!(id >= begin && id < end)) id = -1;
         ids[j] = id;
+      }
+      if (base + nt * IB < hl) {  // the next batch of ids is on its way while this one is inserted
+#pragma unroll
+        for (int j = 0; j < IB; ++j) {
+          const int i = base + nt * IB + j * nt + tid;
+          pre_ids[j] = i < hl ? hist_ids[i] : -1;
+        }
       }
 #pragma unroll
       for (int j = 0; j < IB; ++j) raw[j] = (fetch && ids[j] >= 0) ? row[ids[j]] : 0.0f;
@@ -1000,7 +1141,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   bool list_ok = true;
   if (listed) {
     // the filter already streamed the row: candidates come from its list and from the history
-    list_ok = list_load<PEN>(P, rc, c, h, b, t);
+    list_ok = list_load<PEN>(P, rc, c, h, b, t, pre_count, pre_pair);
     PHASE_MARK(1);
     if (PEN && P.history && list_ok && !rc.lowers) slice_history<PEN>(P, rc, c, h, row, seen_row, begin, end, t);
     PHASE_MARK(2);
