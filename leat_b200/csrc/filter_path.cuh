@@ -189,10 +189,12 @@ __global__ void __launch_bounds__(FILTER_THREADS, 4) filter_kernel(const __grid_
 // sample_kernel's replacement for the stream on a row that has a list: the listed logits become
 // (score, id) keys in the candidate buffer, history tokens among them penalised, and the greedy
 // best among them is tracked.  `listed` is the list's length and first_pair this thread's entry of
-// the first round, both loaded by the caller ahead of time.  False if the list ran over.
+// the first round, both loaded by the caller ahead of time; `bitmap`, if not null, marks the
+// history tokens (then only membership matters).  False if the list ran over.
 template <bool PEN>
 __device__ __noinline__ bool list_load(const KParams& P, const RowCfg& rc, const Ctx& c, const History& h,
-                                       int b, Tracked& t, int listed, unsigned long long first_pair) {
+                                       const unsigned* bitmap, int b, Tracked& t, int listed,
+                                       unsigned long long first_pair) {
   Shared& sm = *c.sm;
   const int tid = threadIdx.x, nt = blockDim.x;
   if (listed > P.list_cap) return false;
@@ -211,7 +213,7 @@ __device__ __noinline__ bool list_load(const KParams& P, const RowCfg& rc, const
       if (PEN && P.history) {
         // a history token: penalised here if penalties only lower logits (then those that matter are
         // all listed), else left to the history pass, which fetches every history token's logit
-        const int count = history_count(h, idx);
+        const int count = bitmap ? (int)((bitmap[idx >> 5] >> (idx & 31)) & 1u) : history_count(h, idx);
         if (count) {
           if (rc.lowers) l = penalised(l, count, rc);
           else skip = true;

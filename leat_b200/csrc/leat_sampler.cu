@@ -128,6 +128,8 @@ Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool
     if (stages >= 2) p.ring_stages = stages;
   }
   p.shared = (int)shared_bytes(h->cap, h->keep, p.bm_words, p.ht_size, (size_t)p.ring_stages * p.threads * RING_PER_THREAD * 4);
+  // words of the area behind the hash keys: room for a bitmap over the vocabulary
+  p.bm_words = (int)((p.shared - fixed_shared(h->cap, h->keep) - ((size_t)p.ht_size * 4 + 127) / 128 * 128) / 4);
   return p;
 }
 

@@ -1077,7 +1077,11 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   for (int i = tid; i < BINS; i += nt) M.hist[i] = 0u;
   if (PEN && P.history) {
 #pragma unroll 1
-    for (int i = tid; i < P.ht_size; i += nt) { hkeys[i] = HASH_EMPTY; hcnt[i] = 0; }
+    for (int i = tid; i < P.ht_size; i += nt) hkeys[i] = HASH_EMPTY;
+    // the counts, or the bitmap a listed row may use in their place: the same bytes
+    const int zero = max(P.ht_size, P.list ? min(P.bm_words, (P.vocab + 31) >> 5) : 0);
+#pragma unroll 1
+    for (int i = tid; i < zero; i += nt) hcnt[i] = 0;
   }
   __syncthreads();
   SETUP_MARK(8);
@@ -1089,6 +1093,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     S = 1;
     end = P.vocab;
   }
+  unsigned* bitmap = nullptr;
   if (PEN && P.history) {
     // the slice's history tokens: a hash table of counts, and each token's logit fetched now (one
     // scattered load each, issued in batches) so the later passes never wait on them
@@ -1096,8 +1101,20 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     // a listed row whose penalties only lower logits finds every history token that matters in its
     // list, logit included: nothing to fetch
     const bool fetch = !(listed && rc.lowers);
+    // ... and if only membership matters (no frequency penalty), a bitmap over the vocabulary says
+    // it with one fire-and-forget atomic per history token instead of a probe sequence
+    if (!fetch && rc.freq == 0.0f && P.vocab <= P.bm_words * 32) bitmap = reinterpret_cast<unsigned*>(hcnt);
 #pragma unroll 1
-    for (int base = 0; base < hl; base += nt * IB) {
+    for (int base = 0; base < (bitmap ? hl : 0); base += nt * IB) {
+#pragma unroll
+      for (int j = 0; j < IB; ++j) {
+        const int i = base + j * nt + tid;
+        const int id = i < hl ? (base == 0 ? pre_ids[j] : hist_ids[i]) - P.vocab_offset : -1;
+        if (id >= 0 && id < end) atomicOr(&bitmap[id >> 5], 1u << (id & 31));
+      }
+    }
+#pragma unroll 1
+    for (int base = 0; base < (bitmap ? 0 : hl); base += nt * IB) {
       int ids[IB];
       float raw[IB];
 #pragma unroll
@@ -1141,7 +1158,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   bool list_ok = true;
   if (listed) {
     // the filter already streamed the row: candidates come from its list and from the history
-    list_ok = list_load<PEN>(P, rc, c, h, b, t, pre_count, pre_pair);
+    list_ok = list_load<PEN>(P, rc, c, h, bitmap, b, t, pre_count, pre_pair);
     PHASE_MARK(1);
     if (PEN && P.history && list_ok && !rc.lowers) slice_history<PEN>(P, rc, c, h, row, seen_row, begin, end, t);
     PHASE_MARK(2);
