@@ -167,9 +167,10 @@ __device__ inline void g_descend(const GRow& g, GShared& gs, unsigned* cnt, unsi
   *mass_above = ma;
 }
 
+// One row, by the whole block that calls it (512 threads), in shared memory it may overwrite:
+// G_BINS * 12 + 384 + ht_size * 8 bytes.
 template <bool PEN>
-__global__ void __launch_bounds__(512) general_kernel(const __grid_constant__ KParams P) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+__device__ __noinline__ void general_row(const KParams& P, int b, unsigned char* smem_raw) {
   unsigned long long* mass = reinterpret_cast<unsigned long long*>(smem_raw);
   unsigned* cnt = reinterpret_cast<unsigned*>(mass + G_BINS);
   GShared& gs = *reinterpret_cast<GShared*>(cnt + G_BINS);
@@ -177,8 +178,6 @@ __global__ void __launch_bounds__(512) general_kernel(const __grid_constant__ KP
   int* hkeys = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(&gs) + 384);
   int* hcnt = hkeys + P.ht_size;
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
-  const int b = blockIdx.x;
-  if (!P.ws_flag[b]) return;
   const int V = P.vocab;
   if (tid == 0) {
     rc = row_config(P, b);
@@ -232,7 +231,6 @@ __global__ void __launch_bounds__(512) general_kernel(const __grid_constant__ KP
   __syncthreads();
   const int greedy_id = gs.greedy_key ? key_id(gs.greedy_key) : P.vocab_offset;
   if (tid == 0) {
-    P.ws_flag[b] = 0;
     if (P.out_greedy) P.out_greedy[b] = greedy_id;
     if (P.status) atomicOr(P.status, 1);
   }

@@ -87,7 +87,7 @@ size_t shared_bytes(int cap, int keep, int bm_words, int ht_size, size_t ring = 
   // the hash keys, then one area shared by their counts, the ring and the scratch of the finish
   size_t keys = ((size_t)ht_size * 4 + 127) / 128 * 128;
   size_t counts = (size_t)ht_size * 8;  // counts and the tokens' logits
-  size_t finish = (size_t)cap * 8 + (size_t)(cap / 32) * 4;
+  size_t finish = (size_t)cap * 8 + (size_t)(cap / 16) * 4;  // weights, running sums, segment sums and offsets
   size_t later = counts > ring ? counts : ring;
   if (finish > later) later = finish;
   return fixed_shared(cap, keep) + keys + later;
@@ -128,6 +128,10 @@ Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool
     if (stages >= 2) p.ring_stages = stages;
   }
   p.shared = (int)shared_bytes(h->cap, h->keep, p.bm_words, p.ht_size, (size_t)p.ring_stages * p.threads * RING_PER_THREAD * 4);
+  // a row the single pass cannot settle is redone in place by the multi-pass routine, which lays
+  // out the block's shared memory its own way
+  const int redo = (int)(G_BINS * 12 + 384 + (size_t)p.ht_size * 8);
+  if (p.shared < redo) p.shared = redo;
   // words of the area behind the hash keys: room for a bitmap over the vocabulary
   p.bm_words = (int)((p.shared - fixed_shared(h->cap, h->keep) - ((size_t)p.ht_size * 4 + 127) / 128 * 128) / 4);
   return p;
@@ -219,15 +223,6 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
   int rc = pen ? launch_one<true>(P, plan, stream) : launch_one<false>(P, plan, stream);
   if (rc != LEAT_OK) return rc;
   h->launches += 1;
-  // rows the single pass flagged are finished by the exact multi-pass kernel; its blocks return at
-  // once for every other row
-  if (!(P.flags & 2u) && !P.cand_count) {
-    const int shared = (int)(G_BINS * 12 + 384 + (size_t)plan.ht_size * 8);
-    if (pen) general_kernel<true><<<P.rows, 512, shared, stream>>>(P);
-    else general_kernel<false><<<P.rows, 512, shared, stream>>>(P);
-    if (cuda_failed(cudaGetLastError(), "general_kernel launch")) return LEAT_E_CUDA;
-    h->launches += 1;
-  }
   return LEAT_OK;
 }
 
@@ -268,7 +263,6 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
   h->sm_count = sms > 0 ? sms : 148;
   const int most = 200 * 1024;
   if (allow_shared(sample_kernel<true>, most) || allow_shared(sample_kernel<false>, most) ||
-      allow_shared(general_kernel<true>, most) || allow_shared(general_kernel<false>, most) ||
       allow_shared(finish_candidates_kernel, most)) {
     delete h; return LEAT_E_CUDA;
   }
@@ -512,8 +506,7 @@ int static_setup(int device, StaticDevice** out) {
       return LEAT_E_CUDA;
     h.sm_count = sms > 0 ? sms : 148;
     const int most = 200 * 1024;
-    if (allow_shared(sample_kernel<true>, most) || allow_shared(sample_kernel<false>, most) ||
-        allow_shared(general_kernel<true>, most) || allow_shared(general_kernel<false>, most))
+    if (allow_shared(sample_kernel<true>, most) || allow_shared(sample_kernel<false>, most))
       return LEAT_E_CUDA;
     sd.ready = true;
   }

@@ -109,6 +109,7 @@ struct Shared {
   unsigned long long gbest;  // block max of the greedy key
   unsigned smin;             // block min of score bits (ord32)
   int jstar, ns, pick, nstrict;
+  int redo;  // the finish found the row's list wanting: the multi-pass routine takes the row
   float floor_l, s_floor;  // the filter's floor of a listed row (+inf otherwise) and its score
   int wcount[32];  // raw entries each warp holds in its own region of the buffer
   // the block's best so far, as order-preserving bits: what a logit must reach to be looked at
@@ -563,7 +564,7 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
     finish_simple(P, b, rc.mode, 0ull, 0ull, true);
     return;
   }
-  if (tid == 0) { sm.jstar = 0; sm.ns = 0; sm.pick = NO_ID; sm.best = 0ull; sm.nstrict = 0; }
+  if (tid == 0) { sm.jstar = 0; sm.ns = 0; sm.pick = NO_ID; sm.best = 0ull; sm.nstrict = 0; sm.redo = 0; }
   if (n <= nt) {
     // one key per thread: every warp sorts its 32 keys in registers, then a key's place is its place
     // in its own run plus, for every other run, the number of keys there above it (a binary search)
@@ -584,16 +585,21 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
     __syncthreads();
     if (key != 0ull) {
       int place = lane;
-#pragma unroll 2
-      for (int r = 0; r < nruns; ++r) {
-        if (r == warp) continue;
-        const unsigned long long* a = runs + r * 32;
-        int pos = 0;
+      // four runs at a time, so that four searches' loads are in flight together
+#pragma unroll 1
+      for (int r0 = 0; r0 < nruns; r0 += 4) {
+        int pos[4] = {0, 0, 0, 0};
 #pragma unroll
-        for (int step = 16; step > 0; step >>= 1)
-          if (a[pos + step - 1] > key) pos += step;
-        if (pos == 31 && a[31] > key) pos = 32;
-        place += pos;
+        for (int step = 16; step > 0; step >>= 1) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            if (runs[(r0 + q) * 32 + pos[q] + step - 1] > key) pos[q] += step;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (pos[q] == 31 && runs[(r0 + q) * 32 + 31] > key) pos[q] = 32;
+          if (r0 + q < nruns && r0 + q != warp) place += pos[q];
+        }
       }
       buf[place] = key;  // every key is in registers or in `runs` by now: the front is free
     }
@@ -643,14 +649,16 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
     if (lane == 31) fs[s] = x;
   }
   __syncthreads();
-  if (tid == 0) {
+  if (tid < nseg) {
+    // segment tid starts at the sum, in order, of the segments before it
     float off = 0.0f;
 #pragma unroll 1
-    for (int s = 0; s < nseg; ++s) { float t = fs[s]; fs[s] = off; off = off + t; }
+    for (int s = 0; s < tid; ++s) off = off + fs[s];
+    fs[nseg + tid] = off;
   }
   __syncthreads();
 #pragma unroll 1
-  for (int j = tid; j < n; j += nt) fi[j] = fs[j >> 5] + fi[j];
+  for (int j = tid; j < n; j += nt) fi[j] = fs[nseg + (j >> 5)] + fi[j];
   __syncthreads();
   FIN_MARK(26);
   const float kept = fi[in_k - 1];
@@ -714,7 +722,7 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
       const bool enough = rc.mode == M_SELECT_MINP || sm.nstrict >= rc.k_eff;
       if (!(enough && cut > s_floor)) {
         id = -1;
-        if (!(P.flags & 2u)) P.ws_flag[b] = 1;
+        if (!(P.flags & 2u)) sm.redo = 1;
         else if (P.status) atomicOr(P.status, 4);
       }
     }
@@ -992,6 +1000,8 @@ __device__ __forceinline__ SmemMap smem_map(unsigned char* raw, int cap, int kee
   return m;
 }
 static_assert(sizeof(Shared) <= 256 && sizeof(Ctx) <= 128 && sizeof(RowCfg) <= 128, "fixed shared-memory slots");
+
+#include "general_kernel.cuh"
 
 #ifndef LEAT_MIN_BLOCKS
 #define LEAT_MIN_BLOCKS 2
@@ -1350,12 +1360,24 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     return;
   }
   if (tid == 0 && P.out_greedy) P.out_greedy[b] = key_id(sm.gbest);
+  // a row this kernel could not settle goes through the exact multi-pass routine, here and now
+  const bool may_redo = P.ws_flag != nullptr && !(P.flags & 2u) && !P.cand_count;
+  if (failed && may_redo) {
+    __syncthreads();
+    general_row<PEN>(P, b, smem_raw);
+    return;
+  }
   if (failed || mode < M_SELECT_K) {
     finish_simple(P, b, mode, sm.best, sm.gbest, failed);
     return;
   }
   finish_row(P, rc, b, buf, sm, fw, fi, fs, listed ? neg_inf() : unord32(sm.smin), listed, sm.s_floor);
   PHASE_MARK(7);
+  __syncthreads();
+  if (sm.redo) {
+    __syncthreads();
+    general_row<PEN>(P, b, smem_raw);
+  }
 }
 
 // Finishes rows from candidates gathered from `g_parts` vocabulary slices: one block per row.
@@ -1440,7 +1462,6 @@ __global__ void __launch_bounds__(512) finish_candidates_kernel(const __grid_con
   finish_row(P, rc, b, buf, sm, fw, fi, fs, neg_inf());
 }
 
-#include "general_kernel.cuh"
 
 // leat/engine.py:612-626 on the device: one thread per sequence
 __global__ void verify_kernel(const int* __restrict__ drafted, const int* __restrict__ sampled,
