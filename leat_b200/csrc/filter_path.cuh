@@ -39,36 +39,26 @@ __device__ __forceinline__ int floor_order(int k, int vocab) {
   return (int)ceilf(x + 4.75f * sqrtf(x) + 4.0f);
 }
 
-// One block of 256 threads per row.  Writes the row's floor (+inf for rows that do not use the
-// list: whole-row Gumbel rows, rows for the multi-pass kernel and rows whose list would be long)
-// and clears the row's list.  Rows are 16-byte aligned multiples of four floats, at least
-// SAMPLE_SIZE * 2 long.
-__global__ void __launch_bounds__(SAMPLE_CHUNKS) floor_kernel(const __grid_constant__ KParams P) {
-  __shared__ float maxima[SAMPLE_CHUNKS];
-  __shared__ float sorted[SAMPLE_CHUNKS];
-  __shared__ RowCfg rc;
-  const int b = blockIdx.x, tid = threadIdx.x;
-  const float* row = P.logits + (size_t)b * P.row_stride;
-  const int V = P.vocab;
-  {
+// The descending chunk maxima of a row's sample, by the first SAMPLE_CHUNKS threads of the calling
+// block (every thread of the block must call); `maxima` and `sorted` are SAMPLE_CHUNKS floats of
+// shared memory each.  Rows are 16-byte aligned multiples of four floats, at least 2 * SAMPLE_SIZE
+// long.
+__device__ __forceinline__ void sample_maxima(const float* __restrict__ row, int V, float* maxima, float* sorted) {
+  const int tid = threadIdx.x;
+  if (tid < SAMPLE_CHUNKS) {
     // chunk tid starts at a multiple of 32 logits near tid * V / 256
     const long long at = ((long long)tid * V / SAMPLE_CHUNKS) & ~31ll;
     const float4* src = reinterpret_cast<const float4*>(row + at);
     float4 x[SAMPLE_CHUNK / 4];
 #pragma unroll
     for (int u = 0; u < SAMPLE_CHUNK / 4; ++u) x[u] = __ldg(src + u);
-    if (tid >= SAMPLE_CHUNKS - 32) {  // the last warp fetches the row's options while the sample is on its way
-      uint32_t unused;
-      const RowIn in = row_inputs_warp(P, b, nullptr, unused);
-      if (tid == SAMPLE_CHUNKS - 1) rc = row_config_from(P, in);
-    }
     float m = neg_inf();  // fmaxf drops NaNs
 #pragma unroll
     for (int u = 0; u < SAMPLE_CHUNK / 4; ++u) m = fmaxf(fmaxf(m, fmaxf(x[u].x, x[u].y)), fmaxf(x[u].z, x[u].w));
     maxima[tid] = m;
   }
   __syncthreads();
-  {
+  if (tid < SAMPLE_CHUNKS) {
     // descending order by counting: place = number of maxima ahead of this one
     const float v = maxima[tid];
     int place = 0;
@@ -80,110 +70,144 @@ __global__ void __launch_bounds__(SAMPLE_CHUNKS) floor_kernel(const __grid_const
     sorted[place] = v;
   }
   __syncthreads();
+}
+
+// The row's floor from its sorted sample maxima: +inf for rows that do not use a list (whole-row
+// Gumbel rows, rows for the multi-pass routine and rows whose list would be long).
+__device__ __forceinline__ float floor_from_sample(const RowCfg& rc, int V, int list_cap, const float* sorted) {
+  const int mode = rc.mode;
+  float floor_l = pos_inf();
+  if (mode == M_SELECT_K) {
+    const int j = floor_order(rc.k_eff, V);
+    // the list must also fit: about j * V / sample logits lie above the j-th maximum
+    if (j <= SAMPLE_MAX_ORDER && (long long)j * V / SAMPLE_SIZE * 4 <= (long long)list_cap * 3) floor_l = sorted[j - 1];
+  } else if (mode == M_ARGMAX_L) {
+    floor_l = sorted[3];
+  } else if (mode == M_SELECT_MINP) {
+    // survivors score at least (true top) + log(min_p), and the true top is at least the sample's
+    const float f = logit_floor(scaled(sorted[0], rc) + rc.logm, rc.tf);
+    if (f >= sorted[SAMPLE_MAX_ORDER - 1]) floor_l = f;
+  }
+  if (rc.track && floor_l < pos_inf()) floor_l = fminf(floor_l, sorted[3]);
+  if (!(floor_l > neg_inf())) floor_l = pos_inf();  // a row of mostly -inf: everything would be listed
+  return floor_l;
+}
+
+// One block of 256 + 32 threads per row.  Writes the row's floor and clears the row's list.
+__global__ void __launch_bounds__(SAMPLE_CHUNKS + 32) floor_kernel(const __grid_constant__ KParams P) {
+  __shared__ float maxima[SAMPLE_CHUNKS];
+  __shared__ float sorted[SAMPLE_CHUNKS];
+  __shared__ RowCfg rc;
+  const int b = blockIdx.x, tid = threadIdx.x;
+  if (tid >= SAMPLE_CHUNKS) {  // a warp of its own fetches the row's options while the sample is on its way
+    uint32_t unused;
+    const RowIn in = row_inputs_warp(P, b, nullptr, unused);
+    if (tid == SAMPLE_CHUNKS) rc = row_config_from(P, in);
+  }
+  sample_maxima(P.logits + (size_t)b * P.row_stride, P.vocab, maxima, sorted);
   if (tid == 0) {
-    const int mode = rc.mode;
-    float floor_l = pos_inf();  // nothing is listed
-    if (mode == M_SELECT_K) {
-      const int j = floor_order(rc.k_eff, V);
-      // the list must also fit: about j * V / sample logits lie above the j-th maximum
-      if (j <= SAMPLE_MAX_ORDER && (long long)j * V / SAMPLE_SIZE * 4 <= (long long)P.list_cap * 3) floor_l = sorted[j - 1];
-    } else if (mode == M_ARGMAX_L) {
-      floor_l = sorted[3];
-    } else if (mode == M_SELECT_MINP) {
-      // survivors score at least (true top) + log(min_p), and the true top is at least the sample's
-      const float f = logit_floor(scaled(sorted[0], rc) + rc.logm, rc.tf);
-      if (f >= sorted[SAMPLE_MAX_ORDER - 1]) floor_l = f;
-    }
-    if (rc.track && floor_l < pos_inf()) floor_l = fminf(floor_l, sorted[3]);
-    if (!(floor_l > neg_inf())) floor_l = pos_inf();  // a row of mostly -inf: everything would be listed
-    P.list_floor[b] = floor_l;
+    P.list_floor[b] = floor_from_sample(rc, P.vocab, P.list_cap, sorted);
     P.list_count[b] = 0;
   }
 }
 
+// A warp's finds on their way to a row's list: collected in shared memory (FILTER_STAGE pairs per
+// warp) and appended with one atomic per flush.
+struct FilterStage {
+  unsigned long long* mine;  // this warp's FILTER_STAGE pairs of shared memory
+  int held;                  // pairs collected (the same in every lane)
+  int row;                   // the row they belong to
+};
+
+__device__ __forceinline__ void filter_flush(const KParams& P, FilterStage& st) {
+  const int lane = threadIdx.x & 31;
+  if (st.held > 0) {
+    int at = 0;
+    if (lane == 0) at = atomicAdd(&P.list_count[st.row], st.held);
+    at = __shfl_sync(FULL, at, 0);
+    unsigned long long* list = P.list + (size_t)st.row * P.list_cap;
+    __syncwarp();
+    for (int i = lane; i < st.held; i += 32)
+      if (at + i < P.list_cap) list[at + i] = st.mine[i];
+    __syncwarp();
+  }
+  st.held = 0;
+}
+
+// The block's NT threads compare the logits [base, base + NT * 32) of row st.row, below `limit`,
+// with the row's floor; whole warps call it together.
+template <int NT>
+__device__ __forceinline__ void filter_visit(const KParams& P, FilterStage& st, const float* __restrict__ row,
+                                             int base, int limit, float floor_l) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  constexpr int nt = NT;
+  float4 x[FILTER_VECS];
+#pragma unroll
+  for (int u = 0; u < FILTER_VECS; ++u) {
+    const int i = base + (u * nt + tid) * 4;
+    x[u] = make_float4(neg_inf(), neg_inf(), neg_inf(), neg_inf());
+    if (i < limit) x[u] = __ldcs(reinterpret_cast<const float4*>(row + i));
+  }
+  float m = neg_inf();
+#pragma unroll
+  for (int u = 0; u < FILTER_VECS; ++u) m = fmaxf(fmaxf(m, fmaxf(x[u].x, x[u].y)), fmaxf(x[u].z, x[u].w));
+  const bool hot = m >= floor_l;
+  if (!__any_sync(FULL, hot)) return;
+  int count = 0;
+  if (hot) {
+#pragma unroll
+    for (int u = 0; u < FILTER_VECS; ++u)
+      count += (x[u].x >= floor_l) + (x[u].y >= floor_l) + (x[u].z >= floor_l) + (x[u].w >= floor_l);
+  }
+  int incl = count;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int o = __shfl_up_sync(FULL, incl, d);
+    if (lane >= d) incl += o;
+  }
+  const int total = __shfl_sync(FULL, incl, 31);
+  if (total > FILTER_STAGE) {
+    // more than the stage holds from 1024 logits: the floor is useless for this row; the count is
+    // pushed past the list's capacity, which sends the row to the multi-pass routine
+    if (lane == 0) atomicAdd(&P.list_count[st.row], P.list_cap + 1);
+    return;
+  }
+  if (st.held + total > FILTER_STAGE) filter_flush(P, st);
+  if (hot) {
+    int at = st.held + incl - count;
+#pragma unroll
+    for (int u = 0; u < FILTER_VECS; ++u) {
+      const int i = base + (u * nt + tid) * 4;
+      const float v[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (v[e] >= floor_l) st.mine[at++] = ((unsigned long long)__float_as_uint(v[e]) << 32) | (uint32_t)(i + e);
+    }
+  }
+  st.held += total;
+}
+
 // Streams the logits once.  A work item is FILTER_SPAN consecutive logits of one row; the items
-// are dealt to the blocks in contiguous runs, so a block mostly stays within one row.  Each warp
-// collects its finds in shared memory and appends them to the row's list with one atomic per flush.
+// are dealt to the blocks in contiguous runs, so a block mostly stays within one row.
 __global__ void __launch_bounds__(FILTER_THREADS, 4) filter_kernel(const __grid_constant__ KParams P, int per_row,
                                                                    int items) {
   __shared__ unsigned long long stage[FILTER_THREADS / 32][FILTER_STAGE];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int V = P.vocab;
   const int first = (int)((long long)blockIdx.x * items / gridDim.x);
   const int last = (int)((long long)(blockIdx.x + 1) * items / gridDim.x);
-  unsigned long long* mine = stage[warp];
-  int held = 0;   // pairs in this warp's stage (warp-uniform)
-  int row_of = -1;  // the row they belong to
-
-  auto flush = [&]() {
-    if (held > 0) {
-      int at = 0;
-      if (lane == 0) at = atomicAdd(&P.list_count[row_of], held);
-      at = __shfl_sync(FULL, at, 0);
-      unsigned long long* list = P.list + (size_t)row_of * P.list_cap;
-      __syncwarp();
-      for (int i = lane; i < held; i += 32)
-        if (at + i < P.list_cap) list[at + i] = mine[i];
-      __syncwarp();
-    }
-    held = 0;
-  };
-
+  FilterStage st;
+  st.mine = stage[threadIdx.x >> 5];
+  st.held = 0;
+  st.row = -1;
 #pragma unroll 1
   for (int item = first; item < last; ++item) {
     const int b = item / per_row;
     const int base = (item - b * per_row) * FILTER_SPAN;
-    if (b != row_of) { flush(); row_of = b; }
+    if (b != st.row) { filter_flush(P, st); st.row = b; }
     const float floor_l = __ldg(&P.list_floor[b]);
     if (!(floor_l < pos_inf())) continue;  // the row does not use the list
-    const float* row = P.logits + (size_t)b * P.row_stride;
-    float4 x[FILTER_VECS];
-#pragma unroll
-    for (int u = 0; u < FILTER_VECS; ++u) {
-      const int i = base + (u * FILTER_THREADS + tid) * 4;
-      x[u] = make_float4(neg_inf(), neg_inf(), neg_inf(), neg_inf());
-      if (i < V) x[u] = __ldcs(reinterpret_cast<const float4*>(row + i));
-    }
-    float m = neg_inf();
-#pragma unroll
-    for (int u = 0; u < FILTER_VECS; ++u) m = fmaxf(fmaxf(m, fmaxf(x[u].x, x[u].y)), fmaxf(x[u].z, x[u].w));
-    const bool hot = m >= floor_l;
-    if (__any_sync(FULL, hot)) {
-      int count = 0;
-      if (hot) {
-#pragma unroll
-        for (int u = 0; u < FILTER_VECS; ++u)
-          count += (x[u].x >= floor_l) + (x[u].y >= floor_l) + (x[u].z >= floor_l) + (x[u].w >= floor_l);
-      }
-      int incl = count;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int o = __shfl_up_sync(FULL, incl, d);
-        if (lane >= d) incl += o;
-      }
-      const int total = __shfl_sync(FULL, incl, 31);
-      if (total > FILTER_STAGE) {
-        // more than the stage holds from 1024 logits: the floor is useless for this row; the count
-        // is pushed past the list's capacity, which sends the row to the multi-pass kernel
-        if (lane == 0) atomicAdd(&P.list_count[b], P.list_cap + 1);
-      } else {
-        if (held + total > FILTER_STAGE) flush();
-        if (hot) {
-          int at = held + incl - count;
-#pragma unroll
-          for (int u = 0; u < FILTER_VECS; ++u) {
-            const int i = base + (u * FILTER_THREADS + tid) * 4;
-            const float v[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              if (v[e] >= floor_l) mine[at++] = ((unsigned long long)__float_as_uint(v[e]) << 32) | (uint32_t)(i + e);
-          }
-        }
-        held += total;
-      }
-    }
+    filter_visit<FILTER_THREADS>(P, st, P.logits + (size_t)b * P.row_stride, base, P.vocab, floor_l);
   }
-  flush();
+  filter_flush(P, st);
 }
 
 // sample_kernel's replacement for the stream on a row that has a list: the listed logits become

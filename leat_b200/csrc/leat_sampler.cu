@@ -208,7 +208,7 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
     P.list_count = reinterpret_cast<int*>(h->ws + h->L.list_count);
     P.list_floor = reinterpret_cast<float*>(h->ws + h->L.list_floor);
     P.list_cap = kListCap;
-    floor_kernel<<<P.rows, SAMPLE_CHUNKS, 0, stream>>>(P);
+    floor_kernel<<<P.rows, SAMPLE_CHUNKS + 32, 0, stream>>>(P);
     if (cuda_failed(cudaGetLastError(), "floor_kernel launch")) return LEAT_E_CUDA;
     const int per_row = (P.vocab + FILTER_SPAN - 1) / FILTER_SPAN;
     const int items = per_row * P.rows;
