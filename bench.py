@@ -36,11 +36,10 @@ sys.path.insert(0, str(ROOT))
 FALLBACK_HBM_GBS = 6650.0  # an earlier measurement on this pool, used when MEASURED_PEAKS.json is absent
 NORTH_STAR_HBM_GBS = 8000.0
 L2_BYTES = 126 << 20
-# DRAM bytes the sampling kernel moved per algorithmic byte in the ncu capture summarised in
-# profiles/sample_kernel_c3_160rows.md: (dram__bytes_read.sum + dram__bytes_write.sum) / (B x V x 4)
-# = (189.6 + 14.7) MB / 167.8 MB on 160 rows of the large-batch configuration; traffic grows with
-# the rows and the vocabulary, so it is scaled to the launch being reported
-TRAFFIC_PER_ALGORITHMIC_BYTE = 1.22
+# DRAM bytes filter_kernel moved per algorithmic byte (B x V x 4) in the ncu capture summarised in
+# profiles/filter_kernel_c3_160rows.md; traffic grows with the rows and the vocabulary, so it is
+# scaled to the launch being reported.  None until a capture has been summarised.
+TRAFFIC_PER_ALGORITHMIC_BYTE = None
 
 
 def peak_hbm() -> tuple[float, str]:
@@ -232,6 +231,19 @@ def time_graph(step, steps: int, warmup: int, inner: int) -> float:
     return a.elapsed_time(b) / (replays * inner)
 
 
+def kernel_milliseconds(sampler, dw, steps: int = 12) -> dict:
+    """Median duration of each kernel of a step, from CUDA events the library records on the
+    launching stream around its launches (plain launches, one step per pool buffer)."""
+    sampler.time_kernels(True)
+    rows = []
+    for i in range(steps + 3):
+        dw.step(sampler, i)
+        rows.append(sampler.kernel_times())
+    sampler.time_kernels(False)
+    floor_ms, filter_ms, finish_ms = np.median(np.array(rows[3:]), axis=0)
+    return {"floor_kernel": float(floor_ms), "filter_kernel": float(filter_ms), "sample_kernel": float(finish_ms)}
+
+
 def run_one(args) -> None:
     """One configuration, a few Python-launched steps: the command ncu captures are taken from."""
     import torch
@@ -271,9 +283,14 @@ def run_single(args) -> None:
         ms = time_graph(lambda i, dw=dw: dw.step(sampler, i), steps=max(args.steps, 2 * len(dw.pool)),
                         warmup=args.warmup, inner=len(dw.pool))  # fmt: skip
         gbs = w.logit_bytes / (ms * 1e-3) / 1e9
+        kernels = kernel_milliseconds(sampler, dw)
+        filter_gbs = w.logit_bytes / (kernels["filter_kernel"] * 1e-3) / 1e9 if kernels["filter_kernel"] > 0 else None
         all_configs[WORKLOAD_NAMES[number]] = {
             "rows": w.rows, "vocab": w.vocab, "us_per_step": round(ms * 1e3, 2), "rows_per_s": round(w.rows / (ms * 1e-3)),
             "hbm_gbs": round(gbs, 1), "frac_of_measured": round(gbs / peak, 4), "frac_of_8tbs": round(gbs / NORTH_STAR_HBM_GBS, 4),
+            "kernel_us": {k: round(v * 1e3, 2) for k, v in kernels.items()},
+            "filter_kernel_gbs": None if filter_gbs is None else round(filter_gbs, 1),
+            "filter_kernel_frac_of_measured": None if filter_gbs is None else round(filter_gbs / peak, 4),
         }  # fmt: skip
         if number != 2:
             del dw
@@ -302,9 +319,13 @@ def run_single(args) -> None:
             torch.cuda.current_stream().synchronize()
 
         ms_e2e = time_device(e2e_step, args.steps, args.warmup)
+        kernels = kernel_milliseconds(sampler, dw)
     value = w.rows / (ms * 1e-3)
-    achieved = w.logit_bytes / (ms * 1e-3) / 1e9
+    # the kernel that moves the bytes is filter_kernel: every logit once
+    achieved = w.logit_bytes / (kernels["filter_kernel"] * 1e-3) / 1e9
+    step_achieved = w.logit_bytes / (ms * 1e-3) / 1e9
     traffic = None if TRAFFIC_PER_ALGORITHMIC_BYTE is None else TRAFFIC_PER_ALGORITHMIC_BYTE * w.logit_bytes
+    large = all_configs[WORKLOAD_NAMES[3]]
 
     threads = os.cpu_count() or 1
     cpu_value, cpu_sample = cpu_rows_per_second(w, "U", seconds=12.0, threads=threads)
@@ -316,8 +337,16 @@ def run_single(args) -> None:
                    "l2": dw.l2_note,
                    "timing": "CUDA events around replays of a CUDA graph that holds one step per pool buffer"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": traffic, "peak_kind": peak_kind, "kernel": "sample_kernel",
-                     "algorithmic_bytes_per_launch": w.logit_bytes},
+                     "traffic": traffic, "peak_kind": peak_kind, "kernel": "filter_kernel",
+                     "algorithmic_bytes_per_launch": w.logit_bytes,
+                     "launch_us": kernels["filter_kernel"] * 1e3,
+                     "kernel_us": {k: v * 1e3 for k, v in kernels.items()},
+                     "whole_step": {"achieved": step_achieved, "frac": step_achieved / peak,
+                                    "note": "all three launches of a step under graph replay"},
+                     "large_batch": {"workload": WORKLOAD_NAMES[3], "rows": large["rows"], "vocab": large["vocab"],
+                                     "filter_kernel_gbs": large["filter_kernel_gbs"],
+                                     "filter_kernel_frac": large["filter_kernel_frac_of_measured"],
+                                     "whole_step_gbs": large["hbm_gbs"], "whole_step_frac": large["frac_of_measured"]}},
         "cpu_baseline": {"value": cpu_value, "unit": "rows/s", "cores": threads, "kind": "port", "sample": cpu_sample},
         "e2e": {"value": w.rows / (ms_e2e * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": w.logit_bytes,
                 "d2h_bytes_per_step": w.rows * 4},

@@ -128,6 +128,12 @@ int leat_sampler_plan(const leat_sampler_t* handle, int32_t rows, int32_t vocab,
                       int32_t* threads, int32_t* slices, int32_t* shared_bytes);
 /* Number of kernels the last call on this handle launched (host counter). */
 int leat_sampler_last_launches(const leat_sampler_t* handle);
+/* Measurement aid.  While enabled, leat_sample records CUDA events on the caller's stream around
+   its launches (do not capture such calls in a CUDA graph); leat_sampler_kernel_times waits for
+   the last call and writes three durations in milliseconds: floor_kernel, filter_kernel and
+   sample_kernel (the first two are 0 when the filter path was not taken). */
+int leat_sampler_time_kernels(leat_sampler_t* handle, int32_t enabled);
+int leat_sampler_kernel_times(leat_sampler_t* handle, float* milliseconds);
 /* Text of the last CUDA error seen by this library on this thread (host pointer, static). */
 const char* leat_sampler_last_cuda_error(void);
 

@@ -25,6 +25,7 @@ _ERRORS = {
 EXPORTS = [
     "leat_sampler_workspace_bytes", "leat_sampler_create", "leat_sampler_destroy",
     "leat_sampler_tune", "leat_sampler_tune_filter", "leat_sampler_tune_ring", "leat_sampler_plan", "leat_sampler_last_launches",
+    "leat_sampler_time_kernels", "leat_sampler_kernel_times",
     "leat_sampler_last_cuda_error", "leat_sample", "leat_argmax", "leat_cutoff",
     "leat_verify_draft", "leat_topk_local", "leat_sample_from_candidates", "leat_sample_static",
     "leat_candidate_record_bytes", "leat_candidate_record_layout", "leat_sample_from_records",
@@ -71,6 +72,8 @@ def _load() -> C.CDLL:
     lib.leat_sampler_tune_filter.argtypes = [p, i32]
     lib.leat_sampler_plan.argtypes = [p, i32, i32, i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32)]
     lib.leat_sampler_last_launches.argtypes = [p]
+    lib.leat_sampler_time_kernels.argtypes = [p, i32]
+    lib.leat_sampler_kernel_times.argtypes = [p, C.POINTER(C.c_float)]
     lib.leat_sampler_last_cuda_error.restype = C.c_char_p
     lib.leat_sampler_last_cuda_error.argtypes = []
     lib.leat_sample.argtypes = [p, C.POINTER(SampleArgs), p]

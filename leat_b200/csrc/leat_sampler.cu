@@ -64,6 +64,9 @@ int cap_for(int keep) { return keep <= 512 ? 2048 : 4096; }
 struct leat_sampler {
   int device, max_rows, max_vocab, k_max, keep, cap;
   int tune_threads, tune_slices, tune_stages, tune_no_ring, tune_no_filter, has_list;
+  // optional per-kernel timing of a call: events around the floor, the filter and the finish
+  int timing;
+  cudaEvent_t marks[4];
   int sm_count;
   int launches;
   unsigned char* ws;
@@ -208,8 +211,10 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
     P.list_count = reinterpret_cast<int*>(h->ws + h->L.list_count);
     P.list_floor = reinterpret_cast<float*>(h->ws + h->L.list_floor);
     P.list_cap = kListCap;
+    if (h->timing) cudaEventRecord(h->marks[0], stream);
     floor_kernel<<<P.rows, SAMPLE_CHUNKS + 32, 0, stream>>>(P);
     if (cuda_failed(cudaGetLastError(), "floor_kernel launch")) return LEAT_E_CUDA;
+    if (h->timing) cudaEventRecord(h->marks[1], stream);
     const int per_row = (P.vocab + FILTER_SPAN - 1) / FILTER_SPAN;
     const int items = per_row * P.rows;
     const int blocks = items < h->sm_count * 4 ? items : h->sm_count * 4;  // four blocks fit an SM
@@ -217,11 +222,14 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
     if (cuda_failed(cudaGetLastError(), "filter_kernel launch")) return LEAT_E_CUDA;
     h->launches += 2;
   }
+  if (h->timing) cudaEventRecord(h->marks[2], stream);
+  if (h->timing && !filtered) { cudaEventRecord(h->marks[0], stream); cudaEventRecord(h->marks[1], stream); }
   Plan plan = make_plan(h, P.rows, P.vocab, P.history_cap, P.history != nullptr, vec);
   P.slices = plan.slices; P.slice_len = plan.slice_len; P.bm_words = plan.bm_words; P.ht_size = plan.ht_size;
   P.ring_stages = plan.ring_stages;  // 0 unless rows are 16-byte aligned multiples of four floats
   int rc = pen ? launch_one<true>(P, plan, stream) : launch_one<false>(P, plan, stream);
   if (rc != LEAT_OK) return rc;
+  if (h->timing) cudaEventRecord(h->marks[3], stream);
   h->launches += 1;
   return LEAT_OK;
 }
@@ -249,7 +257,7 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
   if (!h) return LEAT_E_ARGUMENT;
   h->device = device; h->max_rows = max_rows; h->max_vocab = max_vocab; h->k_max = k_max;
   h->keep = keep_for(k_max); h->cap = cap_for(h->keep);
-  h->tune_threads = 0; h->tune_slices = 0; h->tune_stages = 0; h->tune_no_ring = 0; h->tune_no_filter = 0; h->has_list = 1; h->launches = 0;
+  h->tune_threads = 0; h->tune_slices = 0; h->tune_stages = 0; h->tune_no_ring = 0; h->tune_no_filter = 0; h->has_list = 1; h->timing = 0; h->launches = 0;
   h->L = layout_for(max_rows, max_vocab, h->keep);
   h->ws = static_cast<unsigned char*>(workspace);
   if (bytes < h->L.total || !aligned(workspace, 256)) { delete h; return LEAT_E_WORKSPACE; }
@@ -275,6 +283,7 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
 }
 
 int leat_sampler_destroy(leat_sampler_t* handle) {
+  if (handle && handle->timing) leat_sampler_time_kernels(handle, 0);
   delete handle;
   return LEAT_OK;
 }
@@ -311,6 +320,27 @@ int leat_sampler_plan(const leat_sampler_t* h, int32_t rows, int32_t vocab, int3
 }
 
 int leat_sampler_last_launches(const leat_sampler_t* h) { return h ? h->launches : 0; }
+
+int leat_sampler_time_kernels(leat_sampler_t* h, int32_t enabled) {
+  if (!h) return LEAT_E_ARGUMENT;
+  if (enabled && !h->timing) {
+    for (int i = 0; i < 4; ++i)
+      if (cuda_failed(cudaEventCreate(&h->marks[i]), "cudaEventCreate")) return LEAT_E_CUDA;
+  } else if (!enabled && h->timing) {
+    for (int i = 0; i < 4; ++i) cudaEventDestroy(h->marks[i]);
+  }
+  h->timing = enabled ? 1 : 0;
+  return LEAT_OK;
+}
+
+int leat_sampler_kernel_times(leat_sampler_t* h, float* milliseconds) {
+  if (!h || !milliseconds || !h->timing) return LEAT_E_ARGUMENT;
+  if (cuda_failed(cudaEventSynchronize(h->marks[3]), "cudaEventSynchronize")) return LEAT_E_CUDA;
+  for (int i = 0; i < 3; ++i)
+    if (cuda_failed(cudaEventElapsedTime(&milliseconds[i], h->marks[i], h->marks[i + 1]), "cudaEventElapsedTime"))
+      return LEAT_E_CUDA;
+  return LEAT_OK;
+}
 
 const char* leat_sampler_last_cuda_error(void) { return g_cuda_error; }
 
@@ -486,7 +516,7 @@ int static_setup(int device, StaticDevice** out) {
     leat_sampler& h = sd.handle;
     h.device = device; h.max_rows = kStaticRows; h.max_vocab = kStaticVocab; h.k_max = kStaticK;
     h.keep = keep_for(kStaticK); h.cap = cap_for(h.keep);
-    h.tune_threads = 0; h.tune_slices = 0; h.tune_stages = 0; h.tune_no_ring = 0; h.tune_no_filter = 0; h.has_list = 0; h.launches = 0;
+    h.tune_threads = 0; h.tune_slices = 0; h.tune_stages = 0; h.tune_no_ring = 0; h.tune_no_filter = 0; h.has_list = 0; h.timing = 0; h.launches = 0;
     Layout& L = h.L;
     L.cells = kStaticCells;
     size_t at = 0;

@@ -97,6 +97,16 @@ class Sampler:
     def tune(self, threads: int = 0, slices: int = 0) -> None:
         _lib.check(_lib.lib.leat_sampler_tune(self.handle, threads, slices), "leat_sampler_tune")
 
+    def time_kernels(self, enabled: bool = True) -> None:
+        """Measurement aid: record CUDA events around the launches of each sample() (not under graph capture)."""
+        _lib.check(_lib.lib.leat_sampler_time_kernels(self.handle, int(enabled)), "leat_sampler_time_kernels")
+
+    def kernel_times(self) -> tuple[float, float, float]:
+        """Milliseconds of floor_kernel, filter_kernel and sample_kernel in the last call (waits for it)."""
+        out = (_lib.C.c_float * 3)()
+        _lib.check(_lib.lib.leat_sampler_kernel_times(self.handle, out), "leat_sampler_kernel_times")
+        return float(out[0]), float(out[1]), float(out[2])
+
     def tune_filter(self, enabled: bool = True) -> None:
         _lib.check(_lib.lib.leat_sampler_tune_filter(self.handle, int(enabled)), "leat_sampler_tune_filter")
 
