@@ -61,4 +61,12 @@ __device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v)
   return v;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start while the kernel before it in the stream still runs; it must not touch what that kernel
+// writes before grid_dependency_wait() returns (the earlier grid complete, its writes visible).
+// grid_launch_dependents() lets the next kernel's blocks be scheduled from here on.  Both do nothing
+// in a kernel launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 }  // namespace leat

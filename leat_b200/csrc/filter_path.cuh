@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(SAMPLE_CHUNKS + 32) floor_kernel(const __grid_
   __shared__ float sorted[SAMPLE_CHUNKS];
   __shared__ RowCfg rc;
   const int b = blockIdx.x, tid = threadIdx.x;
+  grid_launch_dependents();  // the filter's blocks may take their places; they wait for this grid to end
   if (tid >= SAMPLE_CHUNKS) {  // a warp of its own fetches the row's options while the sample is on its way
     uint32_t unused;
     const RowIn in = row_inputs_warp(P, b, nullptr, unused);
@@ -192,6 +193,8 @@ __device__ __forceinline__ void filter_visit(const KParams& P, FilterStage& st, 
 __global__ void __launch_bounds__(FILTER_THREADS, 4) filter_kernel(const __grid_constant__ KParams P, int per_row,
                                                                    int items) {
   __shared__ unsigned long long stage[FILTER_THREADS / 32][FILTER_STAGE];
+  grid_dependency_wait();    // the floors are written
+  grid_launch_dependents();  // blocks that finish rows move in as this grid's blocks leave
   const int first = (int)((long long)blockIdx.x * items / gridDim.x);
   const int last = (int)((long long)(blockIdx.x + 1) * items / gridDim.x);
   FilterStage st;

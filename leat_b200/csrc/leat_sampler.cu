@@ -186,11 +186,32 @@ int pick_vec(const KParams& P) {
   return ok ? 4 : 1;
 }
 
+// A launch that may begin while the kernel before it in the stream still runs (programmatic
+// dependent launch); the kernel itself waits, with grid_dependency_wait(), before it reads what
+// that kernel writes.
+template <typename... Params, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared, cudaStream_t stream,
+                             Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, args...);
+}
+
 template <bool PEN>
 int launch_one(const KParams& P, const Plan& plan, cudaStream_t stream) {
   dim3 grid(plan.slices, P.rows);
-  sample_kernel<PEN><<<grid, plan.threads, plan.shared, stream>>>(P);
-  return cuda_failed(cudaGetLastError(), "sample_kernel launch") ? LEAT_E_CUDA : LEAT_OK;
+  // after a filter launch the blocks may move in early; they wait before they read the lists
+  const cudaError_t e = P.list ? launch_dependent(sample_kernel<PEN>, grid, dim3(plan.threads), (size_t)plan.shared, stream, P)
+                               : (sample_kernel<PEN><<<grid, plan.threads, plan.shared, stream>>>(P), cudaGetLastError());
+  return cuda_failed(e, "sample_kernel launch") ? LEAT_E_CUDA : LEAT_OK;
 }
 
 int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
@@ -218,8 +239,8 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
     const int per_row = (P.vocab + FILTER_SPAN - 1) / FILTER_SPAN;
     const int items = per_row * P.rows;
     const int blocks = items < h->sm_count * 4 ? items : h->sm_count * 4;  // four blocks fit an SM
-    filter_kernel<<<blocks, FILTER_THREADS, 0, stream>>>(P, per_row, items);
-    if (cuda_failed(cudaGetLastError(), "filter_kernel launch")) return LEAT_E_CUDA;
+    if (cuda_failed(launch_dependent(filter_kernel, dim3(blocks), dim3(FILTER_THREADS), 0, stream, P, per_row, items),
+                    "filter_kernel launch")) return LEAT_E_CUDA;
     h->launches += 2;
   }
   if (h->timing) cudaEventRecord(h->marks[2], stream);

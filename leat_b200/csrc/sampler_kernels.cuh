@@ -1048,12 +1048,6 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     }
     pre_hl = P.history_len ? P.history_len[b] : P.history_cap;
   }
-  int pre_count = 0;
-  unsigned long long pre_pair = 0ull;
-  if (P.list && slice == 0) {
-    pre_count = __ldcg(&P.list_count[b]);
-    pre_pair = __ldcg(&P.list[(size_t)b * P.list_cap + tid]);
-  }
   RowCfg& rc = *M.rc;
   Ctx& c = *M.ctx;
   History& h = *M.history;  // in shared memory: the out-of-line stream functions take it by reference
@@ -1102,6 +1096,8 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     if (slice > 0) return;
     S = 1;
     end = P.vocab;
+  } else {
+    grid_dependency_wait();  // nothing to gain from an early start: keep the launches in order
   }
   unsigned* bitmap = nullptr;
   if (PEN && P.history) {
@@ -1168,6 +1164,10 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   bool list_ok = true;
   if (listed) {
     // the filter already streamed the row: candidates come from its list and from the history
+    // everything up to here needed the floors only; the lists are complete when the filter's grid is
+    grid_dependency_wait();
+    const int pre_count = __ldcg(&P.list_count[b]);
+    const unsigned long long pre_pair = __ldcg(&P.list[(size_t)b * P.list_cap + tid]);
     list_ok = list_load<PEN>(P, rc, c, h, bitmap, b, t, pre_count, pre_pair);
     PHASE_MARK(1);
     if (PEN && P.history && list_ok && !rc.lowers) slice_history<PEN>(P, rc, c, h, row, seen_row, begin, end, t);
