@@ -225,8 +225,7 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
   const int vec = pick_vec(P);
   // large aligned rows take the filter path: a floor per row, one streaming filter, then one block
   // per row finishes from the row's list
-  const bool filtered = h->has_list && !h->tune_no_filter && !P.cand_count && vec == 4 && !P.seen &&
-                        P.vocab >= kFilterMinVocab;
+  const bool filtered = h->has_list && !h->tune_no_filter && vec == 4 && !P.seen && P.vocab >= kFilterMinVocab;
   if (filtered) {
     P.list = reinterpret_cast<unsigned long long*>(h->ws + h->L.list);
     P.list_count = reinterpret_cast<int*>(h->ws + h->L.list_count);
@@ -252,6 +251,15 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
   if (rc != LEAT_OK) return rc;
   if (h->timing) cudaEventRecord(h->marks[3], stream);
   h->launches += 1;
+  if (filtered && P.cand_count) {
+    // a shard's rows whose list did not hold up are streamed by a second launch; its blocks leave
+    // at once for every other row
+    P.list = nullptr;
+    P.only_rows = P.cand_count;
+    rc = pen ? launch_one<true>(P, plan, stream) : launch_one<false>(P, plan, stream);
+    if (rc != LEAT_OK) return rc;
+    h->launches += 1;
+  }
   return LEAT_OK;
 }
 

@@ -86,6 +86,8 @@ struct KParams {
   int* ws_flag;                 // (rows): 1 = the row needs the multi-pass kernel
   // the filter path: per row a floor, and the list of (logit, index) pairs at or above it
   unsigned long long* list; int* list_count; float* list_floor; int list_cap;
+  // a second pass over the rows a shard's list could not settle: only rows with only_rows[b] == -2
+  const int* only_rows;
 };
 
 struct RowCfg {
@@ -1028,6 +1030,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
 
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
   const int b = blockIdx.y, slice = blockIdx.x;
+  if (P.only_rows && P.only_rows[b] != -2) return;
   int S = P.slices;
   PHASE_BEGIN();
   const int begin = slice * P.slice_len;
@@ -1065,7 +1068,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     c.region = (P.cap - P.keep) / (nt >> 5);
     sm.n = 0; sm.m = 0; sm.conv = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.best = 0ull; sm.gbest = 0ull;
     sm.vmin = 0xFFFFFFFFu; sm.vmax = 0u; sm.valid = 0; sm.smin2 = 0xFFFFFFFFu; sm.rmin = 0xFFFFFFFFu; sm.rmax = 0u;
-    sm.smin = 0xFFFFFFFFu; sm.is_last = (S == 1);
+    sm.smin = 0xFFFFFFFFu; sm.is_last = (S == 1); sm.nstrict = 0;
     sm.share_greedy = 0u; sm.share_gumbel = 0u; sm.share_min = 0xFFFFFFFFu;
     h.raw = hraw; h.keys = hkeys; h.counts = hcnt; h.mask = P.ht_size - 1; h.begin = begin;
     sm.floor_l = P.list ? __uint_as_float(floor_bits) : __uint_as_float(0x7F800000u);
@@ -1210,7 +1213,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   if ((mode == M_SELECT_K || mode == M_SELECT_MINP) && !sm.overflow) {
     if (listed) {
       // keys already; a few hundred the finish sorts as they are, more are reduced first
-      if (mode == M_SELECT_MINP || sm.n > min(384, P.cap / 2)) buffer_rebuild(c, 0);
+      if (mode == M_SELECT_MINP || sm.n > min(384, P.cap / 2) || (P.cand_count && sm.n > P.cand_cap)) buffer_rebuild(c, 0);
     } else {
       // the stream of a top-k row leaves raw entries behind: the rebuild also turns them into keys
       buffer_rebuild(c, S > 1 ? 3 : 1);
@@ -1220,6 +1223,25 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   const float floor_l = listed ? sm.floor_l : neg_inf();
   // a greedy token is only known if the best candidate reaches the floor (nothing dropped beats it)
   if (listed && rc.track && !(sm.gbest != 0ull && key_value(sm.gbest) >= floor_l)) failed = true;
+  if (listed && P.cand_count) {
+    // A shard hands its candidates on instead of finishing, so the list is checked here: top-k rows
+    // need top_k candidates strictly above the floor's score, min-p rows their own threshold strictly
+    // above it.  A row that fails is marked for a second launch that streams it (count -2).
+    if (!failed && mode == M_SELECT_K) {
+      int above = 0;
+#pragma unroll 1
+      for (int i = tid; i < sm.n; i += nt) above += key_value(buf[i]) > sm.s_floor;
+      above = __reduce_add_sync(FULL, above);
+      if (lane == 0 && above) atomicAdd(&sm.nstrict, above);
+      __syncthreads();
+      if (sm.nstrict < rc.k_eff) failed = true;
+    }
+    if (!failed && mode == M_SELECT_MINP && !(sm.tau > sm.s_floor)) failed = true;
+    if (failed) {
+      if (tid == 0) { P.cand_count[b] = -2; P.cand_best[b] = 0ull; }
+      return;
+    }
+  }
 
   PHASE_MARK(4);
   // ---- publish, and let the last block of the row go on ----

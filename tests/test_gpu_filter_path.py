@@ -132,3 +132,29 @@ def test_filter_path_off_gives_the_same_rows(sampler, device):
         sampler.tune_filter(True)
     for name in ("ids", "greedy", "kept", "cut", "prob_ids", "probs"):
         np.testing.assert_array_equal(getattr(on, name).cpu().numpy(), getattr(off, name).cpu().numpy(), err_msg=name)
+
+
+@pytest.mark.parametrize("mode", ["U", "G"])
+def test_shards_whose_lists_fail_are_streamed_again(device, mode):
+    """Vocabulary shards take the filter path too; a shard row whose list does not hold up is marked
+    and streamed by a second launch, so the gathered candidates are complete either way."""
+    from leat_b200 import workloads
+    from tests.test_gpu_sharded_and_masks import _sharded_on_one_gpu
+
+    rng = np.random.default_rng(9)
+    rows, vocab, parts = 6, 4 * V, 4
+    logits = rng.standard_normal((rows, vocab)).astype(np.float32)
+    at = np.arange(vocab)
+    # shard 0: large logits where its sample never looks; shard 1: only where it does; 2 and 3 plain
+    logits[:, (at < V) & ((at % 256) >= 32)] += 6.0
+    hot = np.flatnonzero((at >= V) & (at < 2 * V) & ((at % 256) < 32))[::50]
+    logits[:, hot] += 9.0
+    options = _options(rows, top_k=60, top_p=0.98)
+    options[1, 0] = 0.0
+    history = rng.integers(0, vocab, (rows, 128)).astype(np.int32)
+    penalties = np.tile(np.array([1.2, 0.1, 0.0], np.float32), (rows, 1))
+    w = workloads.Workload("case", logits, options, penalties, history, rng.random(rows, dtype=np.float32),
+                           np.arange(rows, dtype=np.uint32) + 5, np.full(rows, 9, np.int32))  # fmt: skip
+    got = _sharded_on_one_gpu(device, w, parts, mode)
+    want = helpers.oracle_run(w, mode)
+    helpers.compare(want, got, 64, max_fragile=1)
