@@ -36,10 +36,11 @@ sys.path.insert(0, str(ROOT))
 FALLBACK_HBM_GBS = 6650.0  # an earlier measurement on this pool, used when MEASURED_PEAKS.json is absent
 NORTH_STAR_HBM_GBS = 8000.0
 L2_BYTES = 126 << 20
-# DRAM bytes filter_kernel moved per algorithmic byte (B x V x 4) in the ncu capture summarised in
-# profiles/filter_kernel_c3_160rows.md; traffic grows with the rows and the vocabulary, so it is
-# scaled to the launch being reported.  None until a capture has been summarised.
-TRAFFIC_PER_ALGORITHMIC_BYTE = None
+# DRAM bytes filter_kernel moved per algorithmic byte in the ncu capture summarised in
+# profiles/filter_path_c3_160rows.md: (dram__bytes_read.sum + dram__bytes_write.sum) / (B x V x 4)
+# = (167.79 + 3.37) MB / 167.77 MB on 160 rows of the large-batch configuration; traffic grows with
+# the rows and the vocabulary, so it is scaled to the launch being reported
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.02
 
 
 def peak_hbm() -> tuple[float, str]:
