@@ -135,20 +135,25 @@ __device__ __forceinline__ void filter_flush(const KParams& P, FilterStage& st) 
   st.held = 0;
 }
 
-// The block's NT threads compare the logits [base, base + NT * 32) of row st.row, below `limit`,
-// with the row's floor; whole warps call it together.
+// The block's NT threads load the logits [base, base + NT * 32) of a row, below `limit`: logit e of
+// vector u has index base + (u * NT + tid) * 4 + e; logits past the row's end read as -inf.
 template <int NT>
-__device__ __forceinline__ void filter_visit(const KParams& P, FilterStage& st, const float* __restrict__ row,
-                                             int base, int limit, float floor_l) {
-  const int tid = threadIdx.x, lane = tid & 31;
-  constexpr int nt = NT;
-  float4 x[FILTER_VECS];
+__device__ __forceinline__ void filter_load(float4 (&x)[FILTER_VECS], const float* __restrict__ row, int base, int limit) {
+  const int tid = threadIdx.x;
 #pragma unroll
   for (int u = 0; u < FILTER_VECS; ++u) {
-    const int i = base + (u * nt + tid) * 4;
+    const int i = base + (u * NT + tid) * 4;
     x[u] = make_float4(neg_inf(), neg_inf(), neg_inf(), neg_inf());
     if (i < limit) x[u] = __ldcs(reinterpret_cast<const float4*>(row + i));
   }
+}
+
+// What a thread does with the logits it holds of row st.row: those at or above the floor go to the
+// warp's stage.  Whole warps call it together.
+template <int NT>
+__device__ __forceinline__ void filter_process(const KParams& P, FilterStage& st, const float4 (&x)[FILTER_VECS],
+                                               int base, float floor_l) {
+  const int tid = threadIdx.x, lane = tid & 31;
   float m = neg_inf();
 #pragma unroll
   for (int u = 0; u < FILTER_VECS; ++u) m = fmaxf(fmaxf(m, fmaxf(x[u].x, x[u].y)), fmaxf(x[u].z, x[u].w));
@@ -178,7 +183,7 @@ __device__ __forceinline__ void filter_visit(const KParams& P, FilterStage& st, 
     int at = st.held + incl - count;
 #pragma unroll
     for (int u = 0; u < FILTER_VECS; ++u) {
-      const int i = base + (u * nt + tid) * 4;
+      const int i = base + (u * NT + tid) * 4;
       const float v[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
 #pragma unroll
       for (int e = 0; e < 4; ++e)
@@ -193,22 +198,29 @@ __device__ __forceinline__ void filter_visit(const KParams& P, FilterStage& st, 
 __global__ void __launch_bounds__(FILTER_THREADS, 4) filter_kernel(const __grid_constant__ KParams P, int per_row,
                                                                    int items) {
   __shared__ unsigned long long stage[FILTER_THREADS / 32][FILTER_STAGE];
-  grid_dependency_wait();    // the floors are written
-  grid_launch_dependents();  // blocks that finish rows move in as this grid's blocks leave
   const int first = (int)((long long)blockIdx.x * items / gridDim.x);
   const int last = (int)((long long)(blockIdx.x + 1) * items / gridDim.x);
   FilterStage st;
   st.mine = stage[threadIdx.x >> 5];
   st.held = 0;
   st.row = -1;
+  // the first item's logits are asked for before the floors are waited for: they are the caller's
+  float4 x[FILTER_VECS];
+  if (first < last) {
+    const int b = first / per_row;
+    filter_load<FILTER_THREADS>(x, P.logits + (size_t)b * P.row_stride, (first - b * per_row) * FILTER_SPAN, P.vocab);
+  }
+  grid_dependency_wait();    // the floors are written
+  grid_launch_dependents();  // blocks that finish rows move in as this grid's blocks leave
 #pragma unroll 1
   for (int item = first; item < last; ++item) {
     const int b = item / per_row;
     const int base = (item - b * per_row) * FILTER_SPAN;
     if (b != st.row) { filter_flush(P, st); st.row = b; }
-    const float floor_l = __ldg(&P.list_floor[b]);
+    const float floor_l = __ldcg(&P.list_floor[b]);
     if (!(floor_l < pos_inf())) continue;  // the row does not use the list
-    filter_visit<FILTER_THREADS>(P, st, P.logits + (size_t)b * P.row_stride, base, P.vocab, floor_l);
+    if (item > first) filter_load<FILTER_THREADS>(x, P.logits + (size_t)b * P.row_stride, base, P.vocab);
+    filter_process<FILTER_THREADS>(P, st, x, base, floor_l);
   }
   filter_flush(P, st);
 }

@@ -148,6 +148,11 @@ int fill_params(const leat_sampler* h, const leat_sample_args* a, KParams& P) {
   if (!h || !a) return LEAT_E_ARGUMENT;
   if (a->rows < 0 || a->vocab <= 0) return LEAT_E_ARGUMENT;
   if (a->rows > h->max_rows || a->vocab > h->max_vocab) return LEAT_E_CAPACITY;
+  if (a->rows == 0) {  // nothing to do, and nothing to point at
+    memset(&P, 0, sizeof(P));
+    P.vocab = a->vocab;
+    return LEAT_OK;
+  }
   if (!check_broadcast(a->options, a->options_rows, a->rows) ||
       !check_broadcast(a->seed, a->seed_rows, a->rows) ||
       !check_broadcast(a->position, a->position_rows, a->rows) ||
@@ -377,6 +382,7 @@ int leat_sample(leat_sampler_t* h, const leat_sample_args* a, leat_stream_t stre
   KParams P;
   int rc = fill_params(h, a, P);
   if (rc != LEAT_OK) return rc;
+  if (a->rows == 0) { h->launches = 0; return LEAT_OK; }
   if (!a->out_ids) return LEAT_E_ARGUMENT;
   return launch_sample(h, P, static_cast<cudaStream_t>(stream));
 }

@@ -1,20 +1,23 @@
-// The fused sampler kernel for sm_100a.
+// The sampler's kernels for sm_100a.
 //
-// One launch samples every row.  A row of logits is cut into `slices` contiguous pieces, one
-// thread block each (grid = slices x rows).  A block streams its piece from HBM exactly once with
-// 128-bit loads.  History ids are first scattered into a shared-memory bitmap and a small hash
-// table of counts, so penalties cost one shared-memory word per four logits.  The hot loop only
-// compares raw logits against a conservative threshold; the few that pass (and the penalised ones)
-// take an exact path that applies penalties and temperature and appends (score, id) to a
-// shared-memory candidate buffer.  When the buffer fills, the block rebuilds it around the exact
-// k-th largest score by a radix select and raises the threshold.  The block meets at one barrier
-// per streaming step (the next step's loads are already in flight), which is where it learns
-// whether any warp ran out of buffer.
+// sample_kernel settles rows.  Its grid is (slices, rows); what a block does depends on the row:
 //
-// Each block publishes its candidates to the handle's workspace and takes a ticket; the block
-// that draws a row's last ticket merges the row's candidates with the same select, sorts the few
-// survivors, and finishes the row: top-p inside the top-k by a block scan, the min-p floor, the
-// cut, probabilities, and the draw.  No block ever waits for another.
+//   * A row with a list (filter_path.cuh: a floor per row, every logit compared with it once by
+//     filter_kernel, the few at or above it listed in the workspace) needs one block: history
+//     tokens are marked in a shared-memory bitmap (or counted in a hash table), the listed logits
+//     are penalised, scaled and become (score, id) keys in the candidate buffer, and the row is
+//     finished.  The other blocks of the row return at once.
+//   * Any other row is cut into `slices` contiguous pieces, one block each.  A block streams its
+//     piece from HBM exactly once (through a ring of bulk asynchronous copies, stream_ring.cuh, or
+//     with plain loads), comparing raw logits against a conservative threshold; the few that pass
+//     go to the candidate buffer, which is rebuilt around the k-th largest score by a
+//     coarse-to-fine select whenever it fills.  Each block publishes its candidates to the handle's
+//     workspace and takes a ticket; the block that draws a row's last ticket merges them.
+//
+// Finishing a row (finish_row): sort the few hundred candidates, top-p inside the top-k by a block
+// scan, the min-p floor, the cut, probabilities, and the draw.  A row neither way can settle is
+// redone exactly by the multi-pass routine (general_kernel.cuh) in the same block.  No block ever
+// waits for another block.
 //
 // Semantics follow leat/sampler.py:31-73 and leat/ops.py:496-529 (the exact, sort-based cut).
 #pragma once

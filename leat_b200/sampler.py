@@ -88,8 +88,9 @@ class Sampler:
 
     def __del__(self):
         handle = getattr(self, "handle", None)
-        if handle:
-            _lib.lib.leat_sampler_destroy(handle)
+        library = getattr(_lib, "lib", None) if _lib is not None else None  # gone at interpreter exit
+        if handle and library is not None:
+            library.leat_sampler_destroy(handle)
             self.handle = None
 
     # ---- launch shape -------------------------------------------------------------------------
