@@ -170,19 +170,22 @@ SHAPES_ROWS = {1: 1, 2: 16, 3: 256, 4: 72, 5: 512}
 class DeviceWorkload:
     """A workload resident in HBM, its logits replicated into a pool larger than L2."""
 
-    def __init__(self, w, device, min_pool_bytes=2 * L2_BYTES, max_copies=512):
+    def __init__(self, w, device, min_pool_bytes=2 * L2_BYTES, max_copies=512, dtype=None):
         import torch
 
         self.w, self.device = w, device
-        copies = int(min(max_copies, max(1, -(-min_pool_bytes // w.logit_bytes))))
+        self.logit_bytes = w.logit_bytes if dtype is None else w.logit_bytes // 2
+        copies = int(min(max_copies, max(1, -(-min_pool_bytes // self.logit_bytes))))
         base = torch.as_tensor(w.logits).to(device)
+        if dtype is not None:  # the lm_head's own 16-bit output, read as it is
+            base = base.to(dtype)
         self.pool = [base] + [base.clone() for _ in range(copies - 1)]
         t = lambda x: None if x is None else torch.as_tensor(x).to(device)  # noqa: E731
         self.options, self.penalties, self.history = t(w.options), t(w.penalties), t(w.history)
         self.uniform, self.position = t(w.uniform), t(w.position)
         self.seed = torch.as_tensor(w.seed.astype(np.int64)).to(device).to(torch.uint32)
         self.out = torch.empty((w.rows, 1), dtype=torch.int32, device=device)
-        self.l2_note = ("logits pool of %d buffers (%.0f MB) cycled, larger than L2" % (copies, copies * w.logit_bytes / 1e6)
+        self.l2_note = ("logits pool of %d buffers (%.0f MB) cycled, larger than L2" % (copies, copies * self.logit_bytes / 1e6)
                         if copies > 1 else "inputs larger than L2")  # fmt: skip
 
     def step(self, sampler, i: int):
@@ -278,24 +281,23 @@ def run_single(args) -> None:
 
     # every configuration, device-timed under graph replay (kernel figures)
     all_configs = {}
-    for number in (1, 2, 3, 4, 5):
+    for number, dtype in ((1, None), (2, None), (3, None), (4, None), (5, None), (3, torch.bfloat16)):
         w = workloads.CONFIGS[number]()
-        dw = DeviceWorkload(w, device)
+        dw = DeviceWorkload(w, device, dtype=dtype)
         ms = time_graph(lambda i, dw=dw: dw.step(sampler, i), steps=max(args.steps, 2 * len(dw.pool)),
                         warmup=args.warmup, inner=len(dw.pool))  # fmt: skip
-        gbs = w.logit_bytes / (ms * 1e-3) / 1e9
+        gbs = dw.logit_bytes / (ms * 1e-3) / 1e9
         kernels = kernel_milliseconds(sampler, dw)
-        filter_gbs = w.logit_bytes / (kernels["filter_kernel"] * 1e-3) / 1e9 if kernels["filter_kernel"] > 0 else None
-        all_configs[WORKLOAD_NAMES[number]] = {
+        filter_gbs = dw.logit_bytes / (kernels["filter_kernel"] * 1e-3) / 1e9 if kernels["filter_kernel"] > 0 else None
+        all_configs[WORKLOAD_NAMES[number] + ("" if dtype is None else "_bf16_logits")] = {
             "rows": w.rows, "vocab": w.vocab, "us_per_step": round(ms * 1e3, 2), "rows_per_s": round(w.rows / (ms * 1e-3)),
             "hbm_gbs": round(gbs, 1), "frac_of_measured": round(gbs / peak, 4), "frac_of_8tbs": round(gbs / NORTH_STAR_HBM_GBS, 4),
             "kernel_us": {k: round(v * 1e3, 2) for k, v in kernels.items()},
             "filter_kernel_gbs": None if filter_gbs is None else round(filter_gbs, 1),
             "filter_kernel_frac_of_measured": None if filter_gbs is None else round(filter_gbs / peak, 4),
         }  # fmt: skip
-        if number != 2:
-            del dw
-            torch.cuda.empty_cache()
+        del dw
+        torch.cuda.empty_cache()
 
     # the headline workload: the batched server decode step
     w = workloads.config2()

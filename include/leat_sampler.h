@@ -45,15 +45,19 @@ enum {
 /* flags */
 enum {
   LEAT_FLAG_DIVIDE = 1,        /* scores = logits / T as an IEEE quotient instead of logits * (1 / T) */
-  LEAT_FLAG_NO_FALLBACK = 2    /* caller promises every row has 0 < top_k <= k_max (or is greedy): the
-                                  multi-pass kernel is not launched; a row that needs it gets id -1
+  LEAT_FLAG_NO_FALLBACK = 2,   /* caller promises every row has 0 < top_k <= k_max (or is greedy): the
+                                  multi-pass routine is not run; a row that needs it gets id -1
                                   and LEAT_STATUS_INTERNAL */
+  LEAT_FLAG_LOGITS_BF16 = 4,   /* `logits` points at bfloat16 values (the lm_head's own output) */
+  LEAT_FLAG_LOGITS_F16 = 8     /* `logits` points at float16 values */
 };
 
 /* Arguments of leat_sample; stands in for the arguments of sample() at leat/sampler.py:31-34. */
 typedef struct leat_sample_args {
-  /* logits (rows, vocab) float32, row b at logits + b * row_stride */
-  const float* logits;
+  /* logits (rows, vocab), row b at element b * row_stride: float32, or bfloat16 / float16 with
+     LEAT_FLAG_LOGITS_BF16 / LEAT_FLAG_LOGITS_F16 (then 16-byte aligned rows of a multiple of 8
+     tokens, at least 16384, no dense seen mask: LEAT_E_ARGUMENT otherwise) */
+  const void* logits;
   int32_t rows;
   int32_t vocab;
   int64_t row_stride;

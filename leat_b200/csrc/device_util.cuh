@@ -3,6 +3,9 @@
 // lowers them (exp as exp2(x * log2 e), log as log2(x) * ln 2).  Built with -fmad=false: every
 // product and sum below is rounded separately, as the CPU statement of the algorithm does.
 #pragma once
+#include <cuda_bf16.h>
+#include <type_traits>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 

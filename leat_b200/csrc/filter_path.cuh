@@ -26,7 +26,6 @@ constexpr int SAMPLE_SIZE = SAMPLE_CHUNKS * SAMPLE_CHUNK;
 constexpr int SAMPLE_MAX_ORDER = 96; // deepest order statistic of the chunk maxima that is trusted
 constexpr int FILTER_THREADS = 256;
 constexpr int FILTER_VECS = 8;       // 128-bit loads in flight per thread
-constexpr int FILTER_SPAN = FILTER_THREADS * FILTER_VECS * 4;  // logits of one work item: 8192
 constexpr int FILTER_STAGE = 64;     // pairs a warp collects in shared memory between flushes
 
 __device__ __forceinline__ float pos_inf() { return __uint_as_float(0x7F800000u); }
@@ -39,24 +38,152 @@ __device__ __forceinline__ int floor_order(int k, int vocab) {
   return (int)ceilf(x + 4.75f * sqrtf(x) + 4.0f);
 }
 
+// Logits come as float32, bfloat16 or float16 (KParams::dtype 0, 1, 2); a 16-byte vector holds 4 or
+// 8 of them.  Both 16-bit formats convert to float32 exactly, so everything downstream of a
+// comparison works on the same float32 values the oracle sees.
+struct F32 { static constexpr int PER_VEC = 4; };
+struct BF16 { static constexpr int PER_VEC = 8; };
+struct F16 { static constexpr int PER_VEC = 8; };
+
+template <typename T>
+__device__ __forceinline__ void vec_to_floats(const uint4& v, float (&out)[T::PER_VEC]);
+template <>
+__device__ __forceinline__ void vec_to_floats<F32>(const uint4& v, float (&out)[4]) {
+  out[0] = __uint_as_float(v.x); out[1] = __uint_as_float(v.y); out[2] = __uint_as_float(v.z); out[3] = __uint_as_float(v.w);
+}
+template <>
+__device__ __forceinline__ void vec_to_floats<BF16>(const uint4& v, float (&out)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void vec_to_floats<F16>(const uint4& v, float (&out)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
+// the largest of a vector's logits (NaNs dropped); the 16-bit formats compare packed pairs first
+template <typename T>
+__device__ __forceinline__ float vec_max(const uint4& v);
+template <>
+__device__ __forceinline__ float vec_max<F32>(const uint4& v) {
+  return fmaxf(fmaxf(__uint_as_float(v.x), __uint_as_float(v.y)), fmaxf(__uint_as_float(v.z), __uint_as_float(v.w)));
+}
+template <>
+__device__ __forceinline__ float vec_max<BF16>(const uint4& v) {
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&v.x), b = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+  const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&v.z), d = *reinterpret_cast<const __nv_bfloat162*>(&v.w);
+  const __nv_bfloat162 m = __hmax2(__hmax2(a, b), __hmax2(c, d));
+  return fmaxf(__bfloat162float(m.x), __bfloat162float(m.y));
+}
+template <>
+__device__ __forceinline__ float vec_max<F16>(const uint4& v) {
+  const __half2 a = *reinterpret_cast<const __half2*>(&v.x), b = *reinterpret_cast<const __half2*>(&v.y);
+  const __half2 c = *reinterpret_cast<const __half2*>(&v.z), d = *reinterpret_cast<const __half2*>(&v.w);
+  const __half2 m = __hmax2(__hmax2(a, b), __hmax2(c, d));
+  return fmaxf(__half2float(m.x), __half2float(m.y));
+}
+// how many of a vector's logits reach the floor, and their (float32 bits, index) pairs
+template <typename T>
+__device__ __forceinline__ int vec_count(const uint4& v, float floor_l) {
+  float f[T::PER_VEC];
+  vec_to_floats<T>(v, f);
+  int count = 0;
+#pragma unroll
+  for (int e = 0; e < T::PER_VEC; ++e) count += f[e] >= floor_l;
+  return count;
+}
+template <typename T>
+__device__ __forceinline__ int vec_emit(const uint4& v, float floor_l, unsigned long long* out, int at, int i) {
+  float f[T::PER_VEC];
+  vec_to_floats<T>(v, f);
+#pragma unroll
+  for (int e = 0; e < T::PER_VEC; ++e)
+    if (f[e] >= floor_l) out[at++] = ((unsigned long long)__float_as_uint(f[e]) << 32) | (uint32_t)(i + e);
+  return at;
+}
+// which of a 16-bit vector's eight logits reach the floor, one bit each (out of line: it runs for
+// the few vectors whose packed maximum reaches the floor)
+template <typename T>
+__device__ __noinline__ uint32_t vec_hits(uint4 v, float floor_l) {
+  float f[T::PER_VEC];
+  vec_to_floats<T>(v, f);
+  uint32_t bits = 0u;
+#pragma unroll
+  for (int e = 0; e < T::PER_VEC; ++e) bits |= (f[e] >= floor_l ? 1u : 0u) << e;
+  return bits;
+}
+// the packed maxima of two vectors, pair by pair
+template <typename T>
+__device__ __forceinline__ uint4 packed_max(const uint4& a, const uint4& b);
+template <>
+__device__ __forceinline__ uint4 packed_max<BF16>(const uint4& a, const uint4& b) {
+  uint4 r;
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* q = reinterpret_cast<const __nv_bfloat162*>(&b);
+  __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] = __hmax2(p[i], q[i]);
+  return r;
+}
+template <>
+__device__ __forceinline__ uint4 packed_max<F16>(const uint4& a, const uint4& b) {
+  uint4 r;
+  const __half2* p = reinterpret_cast<const __half2*>(&a);
+  const __half2* q = reinterpret_cast<const __half2*>(&b);
+  __half2* o = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] = __hmax2(p[i], q[i]);
+  return r;
+}
+template <>
+__device__ __forceinline__ uint4 packed_max<F32>(const uint4& a, const uint4& b) {
+  return make_uint4(__float_as_uint(fmaxf(__uint_as_float(a.x), __uint_as_float(b.x))),
+                    __float_as_uint(fmaxf(__uint_as_float(a.y), __uint_as_float(b.y))),
+                    __float_as_uint(fmaxf(__uint_as_float(a.z), __uint_as_float(b.z))),
+                    __float_as_uint(fmaxf(__uint_as_float(a.w), __uint_as_float(b.w))));
+}
+__device__ __forceinline__ uint4 minus_inf_vec(int dtype) {
+  const uint32_t w = dtype == 0 ? 0xFF800000u : (dtype == 1 ? 0xFF80FF80u : 0xFC00FC00u);
+  return make_uint4(w, w, w, w);
+}
+// logit i of row b, whatever the format (scattered single reads: history tokens, the multi-pass routine)
+__device__ __forceinline__ float logit_at(const KParams& P, int b, int i) {
+  const size_t at = (size_t)b * P.row_stride + i;
+  if (P.dtype == 0) return P.logits[at];
+  const unsigned short h = reinterpret_cast<const unsigned short*>(P.logits)[at];
+  if (P.dtype == 1) return __uint_as_float((uint32_t)h << 16);
+  return __half2float(__ushort_as_half(h));
+}
+
 // The descending chunk maxima of a row's sample, by the first SAMPLE_CHUNKS threads of the calling
 // block (every thread of the block must call); `maxima` and `sorted` are SAMPLE_CHUNKS floats of
-// shared memory each.  Rows are 16-byte aligned multiples of four floats, at least 2 * SAMPLE_SIZE
-// long.
-__device__ __forceinline__ void sample_maxima(const float* __restrict__ row, int V, float* maxima, float* sorted) {
+// shared memory each.  Rows are 16-byte aligned whole vectors, at least 2 * SAMPLE_SIZE logits long.
+template <typename T>
+__device__ __forceinline__ void sample_maxima(const void* row, int V, int dtype, float* maxima, float* sorted) {
   const int tid = threadIdx.x;
   if (tid < SAMPLE_CHUNKS) {
     // chunk tid starts at a multiple of 32 logits near tid * V / 256
     const long long at = ((long long)tid * V / SAMPLE_CHUNKS) & ~31ll;
-    const float4* src = reinterpret_cast<const float4*>(row + at);
-    float4 x[SAMPLE_CHUNK / 4];
+    constexpr int VECS = SAMPLE_CHUNK / T::PER_VEC;
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(row) + at * (16 / T::PER_VEC));
+    uint4 x[VECS];
 #pragma unroll
-    for (int u = 0; u < SAMPLE_CHUNK / 4; ++u) x[u] = __ldg(src + u);
+    for (int u = 0; u < VECS; ++u) x[u] = __ldg(src + u);
     float m = neg_inf();  // fmaxf drops NaNs
 #pragma unroll
-    for (int u = 0; u < SAMPLE_CHUNK / 4; ++u) m = fmaxf(fmaxf(m, fmaxf(x[u].x, x[u].y)), fmaxf(x[u].z, x[u].w));
+    for (int u = 0; u < VECS; ++u) m = fmaxf(m, vec_max<T>(x[u]));
     maxima[tid] = m;
   }
+  (void)dtype;
   __syncthreads();
   if (tid < SAMPLE_CHUNKS) {
     // descending order by counting: place = number of maxima ahead of this one
@@ -94,6 +221,7 @@ __device__ __forceinline__ float floor_from_sample(const RowCfg& rc, int V, int 
 }
 
 // One block of 256 + 32 threads per row.  Writes the row's floor and clears the row's list.
+template <typename T>
 __global__ void __launch_bounds__(SAMPLE_CHUNKS + 32) floor_kernel(const __grid_constant__ KParams P) {
   __shared__ float maxima[SAMPLE_CHUNKS];
   __shared__ float sorted[SAMPLE_CHUNKS];
@@ -105,7 +233,8 @@ __global__ void __launch_bounds__(SAMPLE_CHUNKS + 32) floor_kernel(const __grid_
     const RowIn in = row_inputs_warp(P, b, nullptr, unused);
     if (tid == SAMPLE_CHUNKS) rc = row_config_from(P, in);
   }
-  sample_maxima(P.logits + (size_t)b * P.row_stride, P.vocab, maxima, sorted);
+  const unsigned char* row = reinterpret_cast<const unsigned char*>(P.logits) + (size_t)b * P.row_stride * (16 / T::PER_VEC);
+  sample_maxima<T>(row, P.vocab, P.dtype, maxima, sorted);
   if (tid == 0) {
     P.list_floor[b] = floor_from_sample(rc, P.vocab, P.list_cap, sorted);
     P.list_count[b] = 0;
@@ -135,35 +264,46 @@ __device__ __forceinline__ void filter_flush(const KParams& P, FilterStage& st) 
   st.held = 0;
 }
 
-// The block's NT threads load the logits [base, base + NT * 32) of a row, below `limit`: logit e of
-// vector u has index base + (u * NT + tid) * 4 + e; logits past the row's end read as -inf.
-template <int NT>
-__device__ __forceinline__ void filter_load(float4 (&x)[FILTER_VECS], const float* __restrict__ row, int base, int limit) {
+// The block's NT threads load FILTER_VECS 16-byte vectors each of a row, from logit `base` on:
+// logit e of vector u has index base + (u * NT + tid) * PER_VEC + e; past the row's end (`limit`)
+// they read as -inf.
+template <typename T, int NT>
+__device__ __forceinline__ void filter_load(uint4 (&x)[FILTER_VECS], const unsigned char* row, int base, int limit,
+                                            int dtype) {
   const int tid = threadIdx.x;
 #pragma unroll
   for (int u = 0; u < FILTER_VECS; ++u) {
-    const int i = base + (u * NT + tid) * 4;
-    x[u] = make_float4(neg_inf(), neg_inf(), neg_inf(), neg_inf());
-    if (i < limit) x[u] = __ldcs(reinterpret_cast<const float4*>(row + i));
+    const int i = base + (u * NT + tid) * T::PER_VEC;
+    x[u] = minus_inf_vec(dtype);
+    if (i < limit) x[u] = __ldcs(reinterpret_cast<const uint4*>(row + (size_t)i * (16 / T::PER_VEC)));
   }
 }
 
 // What a thread does with the logits it holds of row st.row: those at or above the floor go to the
-// warp's stage.  Whole warps call it together.
-template <int NT>
-__device__ __forceinline__ void filter_process(const KParams& P, FilterStage& st, const float4 (&x)[FILTER_VECS],
-                                               int base, float floor_l) {
+// warp's stage, as (float32 bits, index) pairs.  Whole warps call it together.
+template <typename T, int NT>
+__device__ __forceinline__ void filter_process(const KParams& P, FilterStage& st, const uint4 (&x)[FILTER_VECS], int base,
+                                               float floor_l, const unsigned char* row) {
   const int tid = threadIdx.x, lane = tid & 31;
-  float m = neg_inf();
+  // the largest logit this thread holds: vectors are merged pair by pair first (for the 16-bit
+  // formats two logits per instruction), one vector is widened at the end
+  uint4 top = x[0];
 #pragma unroll
-  for (int u = 0; u < FILTER_VECS; ++u) m = fmaxf(fmaxf(m, fmaxf(x[u].x, x[u].y)), fmaxf(x[u].z, x[u].w));
-  const bool hot = m >= floor_l;
+  for (int u = 1; u < FILTER_VECS; ++u) top = packed_max<T>(top, x[u]);
+  const bool hot = vec_max<T>(top) >= floor_l;
   if (!__any_sync(FULL, hot)) return;
   int count = 0;
+  unsigned long long hits = 0ull;  // 16-bit formats: one bit per logit at or above the floor
   if (hot) {
+    if constexpr (T::PER_VEC == 4) {
 #pragma unroll
-    for (int u = 0; u < FILTER_VECS; ++u)
-      count += (x[u].x >= floor_l) + (x[u].y >= floor_l) + (x[u].z >= floor_l) + (x[u].w >= floor_l);
+      for (int u = 0; u < FILTER_VECS; ++u) count += vec_count<T>(x[u], floor_l);
+    } else {
+#pragma unroll
+      for (int u = 0; u < FILTER_VECS; ++u)
+        if (vec_max<T>(x[u]) >= floor_l) hits |= (unsigned long long)vec_hits<T>(x[u], floor_l) << (8 * u);
+      count = __popcll(hits);
+    }
   }
   int incl = count;
 #pragma unroll
@@ -173,54 +313,67 @@ __device__ __forceinline__ void filter_process(const KParams& P, FilterStage& st
   }
   const int total = __shfl_sync(FULL, incl, 31);
   if (total > FILTER_STAGE) {
-    // more than the stage holds from 1024 logits: the floor is useless for this row; the count is
-    // pushed past the list's capacity, which sends the row to the multi-pass routine
+    // more than the stage holds from one warp's logits: the floor is useless for this row; the
+    // count is pushed past the list's capacity, which sends the row to the multi-pass routine
     if (lane == 0) atomicAdd(&P.list_count[st.row], P.list_cap + 1);
     return;
   }
   if (st.held + total > FILTER_STAGE) filter_flush(P, st);
   if (hot) {
     int at = st.held + incl - count;
+    if constexpr (T::PER_VEC == 4) {
 #pragma unroll
-    for (int u = 0; u < FILTER_VECS; ++u) {
-      const int i = base + (u * NT + tid) * 4;
-      const float v[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (v[e] >= floor_l) st.mine[at++] = ((unsigned long long)__float_as_uint(v[e]) << 32) | (uint32_t)(i + e);
+      for (int u = 0; u < FILTER_VECS; ++u) at = vec_emit<T>(x[u], floor_l, st.mine, at, base + (u * NT + tid) * T::PER_VEC);
+    } else {
+      // the few logits that made it are read again (from L2) by their index: no register array is
+      // indexed by a run-time number
+#pragma unroll 1
+      while (hits) {
+        const int bit = __ffsll((long long)hits) - 1;
+        hits &= hits - 1ull;
+        const int i = base + ((bit >> 3) * NT + tid) * T::PER_VEC + (bit & 7);
+        const unsigned short h = reinterpret_cast<const unsigned short*>(row)[i];
+        const float l = std::is_same<T, BF16>::value ? __uint_as_float((uint32_t)h << 16) : __half2float(__ushort_as_half(h));
+        st.mine[at++] = ((unsigned long long)__float_as_uint(l) << 32) | (uint32_t)i;
+      }
     }
   }
   st.held += total;
 }
 
-// Streams the logits once.  A work item is FILTER_SPAN consecutive logits of one row; the items
-// are dealt to the blocks in contiguous runs, so a block mostly stays within one row.
+// Streams the logits once.  A work item is FILTER_THREADS x FILTER_VECS consecutive vectors of one
+// row (8192 float32 logits or 16384 16-bit ones); the items are dealt to the blocks in contiguous
+// runs, so a block mostly stays within one row.
+template <typename T>
 __global__ void __launch_bounds__(FILTER_THREADS, 4) filter_kernel(const __grid_constant__ KParams P, int per_row,
                                                                    int items) {
   __shared__ unsigned long long stage[FILTER_THREADS / 32][FILTER_STAGE];
+  constexpr int SPAN = FILTER_THREADS * FILTER_VECS * T::PER_VEC;
+  constexpr int BYTES = 16 / T::PER_VEC;
   const int first = (int)((long long)blockIdx.x * items / gridDim.x);
   const int last = (int)((long long)(blockIdx.x + 1) * items / gridDim.x);
+  const unsigned char* logits = reinterpret_cast<const unsigned char*>(P.logits);
   FilterStage st;
   st.mine = stage[threadIdx.x >> 5];
   st.held = 0;
   st.row = -1;
   // the first item's logits are asked for before the floors are waited for: they are the caller's
-  float4 x[FILTER_VECS];
+  uint4 x[FILTER_VECS];
   if (first < last) {
     const int b = first / per_row;
-    filter_load<FILTER_THREADS>(x, P.logits + (size_t)b * P.row_stride, (first - b * per_row) * FILTER_SPAN, P.vocab);
+    filter_load<T, FILTER_THREADS>(x, logits + (size_t)b * P.row_stride * BYTES, (first - b * per_row) * SPAN, P.vocab, P.dtype);
   }
   grid_dependency_wait();    // the floors are written
   grid_launch_dependents();  // blocks that finish rows move in as this grid's blocks leave
 #pragma unroll 1
   for (int item = first; item < last; ++item) {
     const int b = item / per_row;
-    const int base = (item - b * per_row) * FILTER_SPAN;
+    const int base = (item - b * per_row) * SPAN;
     if (b != st.row) { filter_flush(P, st); st.row = b; }
     const float floor_l = __ldcg(&P.list_floor[b]);
     if (!(floor_l < pos_inf())) continue;  // the row does not use the list
-    if (item > first) filter_load<FILTER_THREADS>(x, P.logits + (size_t)b * P.row_stride, base, P.vocab);
-    filter_process<FILTER_THREADS>(P, st, x, base, floor_l);
+    if (item > first) filter_load<T, FILTER_THREADS>(x, logits + (size_t)b * P.row_stride * BYTES, base, P.vocab, P.dtype);
+    filter_process<T, FILTER_THREADS>(P, st, x, base, floor_l, logits + (size_t)b * P.row_stride * BYTES);
   }
   filter_flush(P, st);
 }

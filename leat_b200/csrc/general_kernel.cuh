@@ -34,7 +34,7 @@ struct GShared {
 struct GRow {
   const KParams* P;
   const RowCfg* rc;
-  const float* row;
+  int b;  // the row
   const uint8_t* seen_row;
   History h;
   int vocab;
@@ -42,7 +42,7 @@ struct GRow {
 
 // score of token i (penalties, temperature) and whether it counts (NaN scores do not)
 __device__ __forceinline__ bool g_score(const GRow& g, int i, float& l_out, float& s_out) {
-  float l = g.row[i];
+  float l = logit_at(*g.P, g.b, i);
   int count = g.P->history ? history_count(g.h, i) : 0;
   if (g.seen_row && g.seen_row[i]) count = max(count, 1);
   if (count) l = penalised(l, count, *g.rc);
@@ -185,7 +185,7 @@ __device__ __noinline__ void general_row(const KParams& P, int b, unsigned char*
     gs.valid = 0u; gs.live = 0u; gs.live_mass = 0ull; gs.found_id = 0xFFFFFFFFu;
   }
   GRow g;
-  g.P = &P; g.rc = &rc; g.row = P.logits + (size_t)b * P.row_stride; g.vocab = V;
+  g.P = &P; g.rc = &rc; g.b = b; g.vocab = V;
   g.seen_row = (PEN && P.seen) ? P.seen + (size_t)b * P.seen_stride : nullptr;
   g.h.raw = nullptr; g.h.keys = hkeys; g.h.counts = hcnt; g.h.mask = P.ht_size - 1; g.h.begin = 0;
   if (PEN && P.history) {

@@ -162,7 +162,7 @@ int fill_params(const leat_sampler* h, const leat_sample_args* a, KParams& P) {
   if (a->history && a->history_cap > 8192) return LEAT_E_CAPACITY;
   if ((a->out_probs || a->out_prob_ids) && a->out_width <= 0) return LEAT_E_ARGUMENT;
   memset(&P, 0, sizeof(P));
-  P.logits = a->logits; P.rows = a->rows; P.vocab = a->vocab; P.row_stride = a->row_stride;
+  P.logits = static_cast<const float*>(a->logits); P.rows = a->rows; P.vocab = a->vocab; P.row_stride = a->row_stride;
   P.vocab_total = a->vocab_total > 0 ? a->vocab_total : a->vocab;
   P.options = a->options; P.options_rows = a->options_rows;
   P.seed = a->seed; P.seed_rows = a->seed_rows;
@@ -172,6 +172,8 @@ int fill_params(const leat_sampler* h, const leat_sample_args* a, KParams& P) {
   P.penalties = a->penalties; P.penalties_rows = a->penalties_rows;
   P.uniform = a->uniform;
   P.vocab_offset = a->vocab_offset; P.flags = a->flags;
+  if ((a->flags & LEAT_FLAG_LOGITS_BF16) && (a->flags & LEAT_FLAG_LOGITS_F16)) return LEAT_E_ARGUMENT;
+  P.dtype = (a->flags & LEAT_FLAG_LOGITS_BF16) ? 1 : ((a->flags & LEAT_FLAG_LOGITS_F16) ? 2 : 0);
   P.out_ids = a->out_ids; P.out_greedy = a->out_greedy; P.out_cut = a->out_cut; P.out_kept = a->out_kept;
   P.out_probs = a->out_probs; P.out_prob_ids = a->out_prob_ids; P.out_width = a->out_width;
   P.status = a->status;
@@ -186,7 +188,8 @@ int fill_params(const leat_sampler* h, const leat_sample_args* a, KParams& P) {
 }
 
 int pick_vec(const KParams& P) {
-  bool ok = P.vocab % 4 == 0 && P.row_stride % 4 == 0 && aligned(P.logits, 16);
+  const int per_vec = P.dtype == 0 ? 4 : 8;  // logits in 16 bytes
+  bool ok = P.vocab % per_vec == 0 && P.row_stride % per_vec == 0 && aligned(P.logits, 16);
   if (P.seen) ok = ok && P.seen_stride % 4 == 0 && aligned(P.seen, 4);
   return ok ? 4 : 1;
 }
@@ -231,20 +234,28 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
   // large aligned rows take the filter path: a floor per row, one streaming filter, then one block
   // per row finishes from the row's list
   const bool filtered = h->has_list && !h->tune_no_filter && vec == 4 && !P.seen && P.vocab >= kFilterMinVocab;
+  // 16-bit logits are read by the filter path only (and, row by row, by the multi-pass routine)
+  if (P.dtype != 0 && (!filtered || P.cand_count)) return LEAT_E_ARGUMENT;
   if (filtered) {
     P.list = reinterpret_cast<unsigned long long*>(h->ws + h->L.list);
     P.list_count = reinterpret_cast<int*>(h->ws + h->L.list_count);
     P.list_floor = reinterpret_cast<float*>(h->ws + h->L.list_floor);
     P.list_cap = kListCap;
     if (h->timing) cudaEventRecord(h->marks[0], stream);
-    floor_kernel<<<P.rows, SAMPLE_CHUNKS + 32, 0, stream>>>(P);
+    if (P.dtype == 0) floor_kernel<F32><<<P.rows, SAMPLE_CHUNKS + 32, 0, stream>>>(P);
+    else if (P.dtype == 1) floor_kernel<BF16><<<P.rows, SAMPLE_CHUNKS + 32, 0, stream>>>(P);
+    else floor_kernel<F16><<<P.rows, SAMPLE_CHUNKS + 32, 0, stream>>>(P);
     if (cuda_failed(cudaGetLastError(), "floor_kernel launch")) return LEAT_E_CUDA;
     if (h->timing) cudaEventRecord(h->marks[1], stream);
-    const int per_row = (P.vocab + FILTER_SPAN - 1) / FILTER_SPAN;
+    const int span = FILTER_THREADS * FILTER_VECS * (P.dtype == 0 ? 4 : 8);  // logits of one work item
+    const int per_row = (P.vocab + span - 1) / span;
     const int items = per_row * P.rows;
     const int blocks = items < h->sm_count * 4 ? items : h->sm_count * 4;  // four blocks fit an SM
-    if (cuda_failed(launch_dependent(filter_kernel, dim3(blocks), dim3(FILTER_THREADS), 0, stream, P, per_row, items),
-                    "filter_kernel launch")) return LEAT_E_CUDA;
+    const cudaError_t e =
+        P.dtype == 0 ? launch_dependent(filter_kernel<F32>, dim3(blocks), dim3(FILTER_THREADS), 0, stream, P, per_row, items)
+        : P.dtype == 1 ? launch_dependent(filter_kernel<BF16>, dim3(blocks), dim3(FILTER_THREADS), 0, stream, P, per_row, items)
+                       : launch_dependent(filter_kernel<F16>, dim3(blocks), dim3(FILTER_THREADS), 0, stream, P, per_row, items);
+    if (cuda_failed(e, "filter_kernel launch")) return LEAT_E_CUDA;
     h->launches += 2;
   }
   if (h->timing) cudaEventRecord(h->marks[2], stream);

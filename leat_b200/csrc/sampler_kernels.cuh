@@ -62,6 +62,7 @@ constexpr float GUMBEL_MAX = 17.0f;  // above -log(-log(1 - 2^-24)) = 16.64
 
 struct KParams {
   const float* logits; int rows; int vocab; long long row_stride; int vocab_total;
+  int dtype;  // what `logits` really points at: 0 float32, 1 bfloat16, 2 float16 (row_stride in logits)
   const float* options; int options_rows;
   const float* opt_k; const float* opt_p; const float* opt_m;  // leat_cutoff: separate columns, T = 1
   const uint32_t* seed; int seed_rows; const int* position; int position_rows;
@@ -1075,6 +1076,8 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     sm.share_greedy = 0u; sm.share_gumbel = 0u; sm.share_min = 0xFFFFFFFFu;
     h.raw = hraw; h.keys = hkeys; h.counts = hcnt; h.mask = P.ht_size - 1; h.begin = begin;
     sm.floor_l = P.list ? __uint_as_float(floor_bits) : __uint_as_float(0x7F800000u);
+    // the streaming code reads float32 only: a 16-bit row without a list is left to the multi-pass routine
+    if (P.dtype != 0 && !(sm.floor_l < __uint_as_float(0x7F800000u))) { rc.mode = M_GENERAL; c.mode = M_GENERAL; }
     sm.s_floor = neg_inf();
     if (sm.floor_l < __uint_as_float(0x7F800000u)) {
       // nothing scoring under the floor can matter to a row whose list stands
@@ -1144,7 +1147,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
         }
       }
 #pragma unroll
-      for (int j = 0; j < IB; ++j) raw[j] = (fetch && ids[j] >= 0) ? row[ids[j]] : 0.0f;
+      for (int j = 0; j < IB; ++j) raw[j] = (fetch && ids[j] >= 0) ? logit_at(P, b, ids[j]) : 0.0f;
 #pragma unroll
       for (int j = 0; j < IB; ++j) {
         const int id = ids[j];

@@ -128,8 +128,10 @@ class Sampler:
 
     def _args(self, logits, options, seed, position, seen, history, history_len, penalties, uniform,
               flags, vocab_offset=0, vocab_total=0) -> tuple[_lib.SampleArgs, list]:  # fmt: skip
-        if logits.dim() != 2 or logits.dtype != torch.float32 or not logits.is_cuda:
-            raise ValueError("logits must be a (B, V) float32 CUDA tensor")
+        formats = {torch.float32: 0, torch.bfloat16: _lib.FLAG_LOGITS_BF16, torch.float16: _lib.FLAG_LOGITS_F16}
+        if logits.dim() != 2 or logits.dtype not in formats or not logits.is_cuda:
+            raise ValueError("logits must be a (B, V) float32, bfloat16 or float16 CUDA tensor")
+        flags |= formats[logits.dtype]
         if logits.stride(1) != 1:
             logits = logits.contiguous()
         rows, vocab = logits.shape

@@ -197,3 +197,52 @@ def test_full_size_config5_properties(sampler, device):
             assert ids[b] == want.ids[i, 0] and kept[b] == want.kept[i]
             np.testing.assert_array_equal(prob_ids[b, : kept[b]], want.prob_ids[i])
             np.testing.assert_allclose(probs[b, : kept[b]], want.probs[i], rtol=helpers.PROB_RTOL)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("mode", ["U", "G"])
+def test_sixteen_bit_logits(sampler, device, dtype, mode):
+    """bfloat16 and float16 logits (an lm_head's own output) are read as they are; both convert to
+    float32 exactly, so the oracle on the converted values is the answer.  Rows without a list (no
+    cut at all, top-p over the whole vocabulary) go through the multi-pass routine."""
+    import torch
+
+    rng = np.random.default_rng(21)
+    rows, vocab = 8, 65536
+    raw = torch.as_tensor((rng.standard_normal((rows, vocab)) * 3).astype(np.float32))
+    raw[:, :50] += 6.0
+    narrow = raw.to(getattr(torch, dtype))
+    logits = narrow.to(torch.float32).numpy()  # what the sampler must see
+    options = _options(rows, top_k=50, top_p=0.9)
+    options[1, 0] = 0.0
+    options[2] = (0.8, 0, 0.9, 0.0, 0.0)  # top-p with no top-k: multi-pass
+    options[3] = (1.0, 0, 1.0, 0.0, 0.0)  # no cut at all
+    options[4] = (0.7, 0, 1.0, 0.05, 0.0)  # min-p only
+    history = rng.integers(0, vocab, (rows, 96)).astype(np.int32)
+    history[:, :6] = np.argsort(-logits, axis=1)[:, :6]
+    penalties = np.tile(np.array([1.2, 0.3, 0.1], np.float32), (rows, 1))
+    penalties[6] = (0.9, 0.0, 0.0)  # raises logits: history tokens are fetched one by one
+    w = _workload(logits, options, history=history, penalties=penalties)
+    got = helpers.gpu_run(sampler, w, mode, device, width=0, logits=narrow.to(device))
+    want = helpers.oracle_run(w, mode, order="sequential")
+    torch.cuda.synchronize()
+    assert int(got.status.item()) & 4 == 0
+    ids, kept, cut = got.ids.cpu().numpy().ravel(), got.kept.cpu().numpy(), got.cut.cpu().numpy()
+    np.testing.assert_array_equal(got.greedy.cpu().numpy(), want.greedy)
+    soft = 0
+    for b in range(rows):
+        greedy_row = not options[b, 0] > 0
+        ok = ids[b] == want.ids[b, 0] and (greedy_row or (kept[b] == want.kept[b] and cut[b] == want.cut[b]))
+        if not ok:
+            assert want.margin[b] < 1e-4, (b, ids[b], want.ids[b, 0], kept[b], want.kept[b], cut[b], want.cut[b])
+            soft += 1
+    assert soft <= 1
+
+
+def test_sixteen_bit_logits_need_the_filter_path(sampler, device):
+    import torch
+
+    logits = torch.zeros((2, 1000), dtype=torch.bfloat16, device=device)  # too narrow for a list
+    with pytest.raises(ValueError):
+        sampler.sample_full(logits, torch.as_tensor(_options(2)).to(device), torch.zeros(2, dtype=torch.int32).to(device).to(torch.uint32),
+                            torch.zeros(2, dtype=torch.int32, device=device))  # fmt: skip
