@@ -3,7 +3,7 @@
 //
 // Three launches instead of one fused kernel doing everything per block:
 //
-//   floor_kernel   one block per row reads a spread-out sample of the row (256 chunks of 32 logits,
+//   floor_kernel   one block per row reads a spread-out sample of the row (256 chunks of 128 bytes,
 //                  32 KB) and takes a low order statistic of the chunks' maxima as the row's floor:
 //                  a raw logit above which, with overwhelming probability, at least top_k logits of
 //                  the row lie, and not many more.
@@ -21,8 +21,8 @@
 #pragma once
 
 constexpr int SAMPLE_CHUNKS = 256;   // chunks of the sample, one per thread of floor_kernel
-constexpr int SAMPLE_CHUNK = 32;     // logits per chunk (128 bytes)
-constexpr int SAMPLE_SIZE = SAMPLE_CHUNKS * SAMPLE_CHUNK;
+constexpr int SAMPLE_CHUNK_BYTES = 128;  // a chunk is one 128-byte line: 32 float32 logits, 64 16-bit ones
+constexpr int SAMPLE_SIZE = SAMPLE_CHUNKS * 32;  // logits of a float32 row's sample (16-bit rows: twice that)
 constexpr int SAMPLE_MAX_ORDER = 96; // deepest order statistic of the chunk maxima that is trusted
 constexpr int FILTER_THREADS = 256;
 constexpr int FILTER_VECS = 8;       // 128-bit loads in flight per thread
@@ -33,8 +33,8 @@ __device__ __forceinline__ float pos_inf() { return __uint_as_float(0x7F800000u)
 // Which order statistic of the sample bounds the top k of the row from below.  x = k * sample / V
 // sample elements are expected among the row's top k; the number that really are is close to
 // Poisson(x), and j is chosen so that fewer than j are with probability about 1 - 1e-6.
-__device__ __forceinline__ int floor_order(int k, int vocab) {
-  const float x = (float)k * (float)SAMPLE_SIZE / (float)vocab;
+__device__ __forceinline__ int floor_order(int k, int vocab, int sample) {
+  const float x = (float)k * (float)sample / (float)vocab;
   return (int)ceilf(x + 4.75f * sqrtf(x) + 4.0f);
 }
 
@@ -91,27 +91,8 @@ __device__ __forceinline__ float vec_max<F16>(const uint4& v) {
   const __half2 m = __hmax2(__hmax2(a, b), __hmax2(c, d));
   return fmaxf(__half2float(m.x), __half2float(m.y));
 }
-// how many of a vector's logits reach the floor, and their (float32 bits, index) pairs
-template <typename T>
-__device__ __forceinline__ int vec_count(const uint4& v, float floor_l) {
-  float f[T::PER_VEC];
-  vec_to_floats<T>(v, f);
-  int count = 0;
-#pragma unroll
-  for (int e = 0; e < T::PER_VEC; ++e) count += f[e] >= floor_l;
-  return count;
-}
-template <typename T>
-__device__ __forceinline__ int vec_emit(const uint4& v, float floor_l, unsigned long long* out, int at, int i) {
-  float f[T::PER_VEC];
-  vec_to_floats<T>(v, f);
-#pragma unroll
-  for (int e = 0; e < T::PER_VEC; ++e)
-    if (f[e] >= floor_l) out[at++] = ((unsigned long long)__float_as_uint(f[e]) << 32) | (uint32_t)(i + e);
-  return at;
-}
-// which of a 16-bit vector's eight logits reach the floor, one bit each (out of line: it runs for
-// the few vectors whose packed maximum reaches the floor)
+// which of a vector's logits reach the floor, one bit each (out of line: it runs for the few
+// vectors whose maximum reaches the floor)
 template <typename T>
 __device__ __noinline__ uint32_t vec_hits(uint4 v, float floor_l) {
   float f[T::PER_VEC];
@@ -166,14 +147,16 @@ __device__ __forceinline__ float logit_at(const KParams& P, int b, int i) {
 
 // The descending chunk maxima of a row's sample, by the first SAMPLE_CHUNKS threads of the calling
 // block (every thread of the block must call); `maxima` and `sorted` are SAMPLE_CHUNKS floats of
-// shared memory each.  Rows are 16-byte aligned whole vectors, at least 2 * SAMPLE_SIZE logits long.
+// shared memory each.  Rows are 16-byte aligned whole vectors, at least 2 * SAMPLE_SIZE logits long
+// (so that the chunks do not overlap).
 template <typename T>
 __device__ __forceinline__ void sample_maxima(const void* row, int V, int dtype, float* maxima, float* sorted) {
   const int tid = threadIdx.x;
   if (tid < SAMPLE_CHUNKS) {
-    // chunk tid starts at a multiple of 32 logits near tid * V / 256
-    const long long at = ((long long)tid * V / SAMPLE_CHUNKS) & ~31ll;
-    constexpr int VECS = SAMPLE_CHUNK / T::PER_VEC;
+    // chunk tid starts at a multiple of its own length near tid * V / 256
+    constexpr int VECS = SAMPLE_CHUNK_BYTES / 16;
+    constexpr long long CHUNK = VECS * T::PER_VEC;  // logits
+    const long long at = ((long long)tid * V / SAMPLE_CHUNKS) & ~(CHUNK - 1);
     const uint4* src = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(row) + at * (16 / T::PER_VEC));
     uint4 x[VECS];
 #pragma unroll
@@ -201,13 +184,13 @@ __device__ __forceinline__ void sample_maxima(const void* row, int V, int dtype,
 
 // The row's floor from its sorted sample maxima: +inf for rows that do not use a list (whole-row
 // Gumbel rows, rows for the multi-pass routine and rows whose list would be long).
-__device__ __forceinline__ float floor_from_sample(const RowCfg& rc, int V, int list_cap, const float* sorted) {
+__device__ __forceinline__ float floor_from_sample(const RowCfg& rc, int V, int sample, int list_cap, const float* sorted) {
   const int mode = rc.mode;
   float floor_l = pos_inf();
   if (mode == M_SELECT_K) {
-    const int j = floor_order(rc.k_eff, V);
+    const int j = floor_order(rc.k_eff, V, sample);
     // the list must also fit: about j * V / sample logits lie above the j-th maximum
-    if (j <= SAMPLE_MAX_ORDER && (long long)j * V / SAMPLE_SIZE * 4 <= (long long)list_cap * 3) floor_l = sorted[j - 1];
+    if (j <= SAMPLE_MAX_ORDER && (long long)j * V / sample * 4 <= (long long)list_cap * 3) floor_l = sorted[j - 1];
   } else if (mode == M_ARGMAX_L) {
     floor_l = sorted[3];
   } else if (mode == M_SELECT_MINP) {
@@ -236,7 +219,7 @@ __global__ void __launch_bounds__(SAMPLE_CHUNKS + 32) floor_kernel(const __grid_
   const unsigned char* row = reinterpret_cast<const unsigned char*>(P.logits) + (size_t)b * P.row_stride * (16 / T::PER_VEC);
   sample_maxima<T>(row, P.vocab, P.dtype, maxima, sorted);
   if (tid == 0) {
-    P.list_floor[b] = floor_from_sample(rc, P.vocab, P.list_cap, sorted);
+    P.list_floor[b] = floor_from_sample(rc, P.vocab, SAMPLE_CHUNKS * (SAMPLE_CHUNK_BYTES / 16) * T::PER_VEC, P.list_cap, sorted);
     P.list_count[b] = 0;
   }
 }
@@ -293,17 +276,12 @@ __device__ __forceinline__ void filter_process(const KParams& P, FilterStage& st
   const bool hot = vec_max<T>(top) >= floor_l;
   if (!__any_sync(FULL, hot)) return;
   int count = 0;
-  unsigned long long hits = 0ull;  // 16-bit formats: one bit per logit at or above the floor
+  unsigned long long hits = 0ull;  // one bit per logit at or above the floor
   if (hot) {
-    if constexpr (T::PER_VEC == 4) {
 #pragma unroll
-      for (int u = 0; u < FILTER_VECS; ++u) count += vec_count<T>(x[u], floor_l);
-    } else {
-#pragma unroll
-      for (int u = 0; u < FILTER_VECS; ++u)
-        if (vec_max<T>(x[u]) >= floor_l) hits |= (unsigned long long)vec_hits<T>(x[u], floor_l) << (8 * u);
-      count = __popcll(hits);
-    }
+    for (int u = 0; u < FILTER_VECS; ++u)
+      if (vec_max<T>(x[u]) >= floor_l) hits |= (unsigned long long)vec_hits<T>(x[u], floor_l) << (T::PER_VEC * u);
+    count = __popcll(hits);
   }
   int incl = count;
 #pragma unroll
@@ -321,21 +299,21 @@ __device__ __forceinline__ void filter_process(const KParams& P, FilterStage& st
   if (st.held + total > FILTER_STAGE) filter_flush(P, st);
   if (hot) {
     int at = st.held + incl - count;
-    if constexpr (T::PER_VEC == 4) {
-#pragma unroll
-      for (int u = 0; u < FILTER_VECS; ++u) at = vec_emit<T>(x[u], floor_l, st.mine, at, base + (u * NT + tid) * T::PER_VEC);
-    } else {
-      // the few logits that made it are read again (from L2) by their index: no register array is
-      // indexed by a run-time number
+    // the few logits that made it are read again (from L2) by their index: no register array is
+    // indexed by a run-time number
 #pragma unroll 1
-      while (hits) {
-        const int bit = __ffsll((long long)hits) - 1;
-        hits &= hits - 1ull;
-        const int i = base + ((bit >> 3) * NT + tid) * T::PER_VEC + (bit & 7);
+    while (hits) {
+      const int bit = __ffsll((long long)hits) - 1;
+      hits &= hits - 1ull;
+      const int i = base + ((bit / T::PER_VEC) * NT + tid) * T::PER_VEC + (bit % T::PER_VEC);
+      float l;
+      if constexpr (T::PER_VEC == 4) {
+        l = reinterpret_cast<const float*>(row)[i];
+      } else {
         const unsigned short h = reinterpret_cast<const unsigned short*>(row)[i];
-        const float l = std::is_same<T, BF16>::value ? __uint_as_float((uint32_t)h << 16) : __half2float(__ushort_as_half(h));
-        st.mine[at++] = ((unsigned long long)__float_as_uint(l) << 32) | (uint32_t)i;
+        l = std::is_same<T, BF16>::value ? __uint_as_float((uint32_t)h << 16) : __half2float(__ushort_as_half(h));
       }
+      st.mine[at++] = ((unsigned long long)__float_as_uint(l) << 32) | (uint32_t)i;
     }
   }
   st.held += total;
