@@ -7,7 +7,7 @@ library raises ImportError: there is no CPU or eager fallback."""
 _LAZY = {
     "Sampling": "sampler", "GREEDY": "sampler", "sample": "sampler", "Sampler": "sampler",
     "Sampled": "sampler", "default_sampler": "sampler", "ops": None, "speculative": None,
-    "sharded": None, "workloads": None,
+    "sharded": None, "workloads": None, "history": None, "SlotHistory": "history",
 }  # fmt: skip
 
 

@@ -155,3 +155,48 @@ def test_sharded_sampler_over_nccl_with_one_rank(device):
         helpers.compare(helpers.oracle_run(w, "U"), got, 64, max_fragile=0)
     finally:
         dist.destroy_process_group()
+
+
+def test_sparse_slot_history_equals_the_dense_mask(device):
+    """leat keeps a dense (slots, vocab) mask of generated tokens; SlotHistory keeps their ids.  A
+    presence penalty through either gives the same tokens, cuts and survivors (the dense mask on
+    the streaming kernel, the ids on the filter path)."""
+    import torch
+
+    from leat_b200.history import SlotHistory, dense_mask
+    from leat_b200.sampler import Sampler
+
+    rng = np.random.default_rng(31)
+    slots, vocab, rows = 8, 50048, 5
+    special = [5, 6, 7]
+    h = SlotHistory(slots, 128, vocab, special_ids=special, device=device)
+    for _ in range(60):
+        which = torch.as_tensor(rng.permutation(slots)[:rows].copy())
+        tokens = rng.integers(0, vocab, rows)
+        tokens[rng.random(rows) < 0.1] = 6
+        h.append(which, torch.as_tensor(tokens))
+    logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+    step_slots = torch.as_tensor([6, 1, 3, 0, 4])
+    history, length = h.rows(step_slots)
+    best = np.argsort(-logits, axis=1)[:, :5]
+    history[:, :5] = torch.as_tensor(best.astype(np.int32)).to(device)  # make the penalty matter
+    length = torch.clamp(length, min=5)
+    seen = dense_mask(history, vocab, length)
+    options = np.tile(np.array([0.8, 40, 0.95, 0.0, 1.5], np.float32), (rows, 1))
+    options[2, 0] = 0.0
+    sampler = Sampler(rows, vocab, 64, device)
+    t = lambda x: torch.as_tensor(x).to(device)  # noqa: E731
+    seed = torch.as_tensor(np.arange(rows, dtype=np.int64)).to(device).to(torch.uint32)
+    position = t(np.full(rows, 7, np.int32))
+    uniform = t(rng.random(rows, dtype=np.float32))
+    penalties = t(np.tile(np.array([1.0, 1.5, 0.0], np.float32), (rows, 1)))
+    sparse = sampler.sample_full(t(logits), t(options), seed, position, history=history, history_len=length,
+                                 penalties=penalties, uniform=uniform, width=40, want_greedy=True, want_cut=True)  # fmt: skip
+    dense = sampler.sample_full(t(logits), t(options), seed, position, seen.to(torch.uint8), uniform=uniform, width=40,
+                                want_greedy=True, want_cut=True)  # fmt: skip
+    torch.cuda.synchronize()
+    for name in ("ids", "greedy", "kept", "cut", "prob_ids", "probs"):
+        a, b = getattr(sparse, name).cpu().numpy(), getattr(dense, name).cpu().numpy()
+        if name == "cut":
+            a, b = a[options[:, 0] > 0], b[options[:, 0] > 0]
+        np.testing.assert_array_equal(a, b, err_msg=name)
