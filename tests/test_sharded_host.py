@@ -76,7 +76,7 @@ def test_two_ranks_agree_with_one_device():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    manager = mp.Manager()
+    manager = mp.get_context("spawn").Manager()
     results = manager.dict()
     mp.spawn(_rank, args=(2, port, results), nprocs=2, join=True)
     w = workloads.config5(rows=ROWS, vocab=VOCAB)
