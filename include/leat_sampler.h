@@ -49,7 +49,9 @@ enum {
                                   multi-pass routine is not run; a row that needs it gets id -1
                                   and LEAT_STATUS_INTERNAL */
   LEAT_FLAG_LOGITS_BF16 = 4,   /* `logits` points at bfloat16 values (the lm_head's own output) */
-  LEAT_FLAG_LOGITS_F16 = 8     /* `logits` points at float16 values */
+  LEAT_FLAG_LOGITS_F16 = 8,    /* `logits` points at float16 values */
+  LEAT_FLAG_CLEAR_STATUS = 16  /* the call clears the status word before its kernels OR into it (saves
+                                  the caller a fill of its own) */
 };
 
 /* Arguments of leat_sample; stands in for the arguments of sample() at leat/sampler.py:31-34. */

@@ -12,7 +12,7 @@ LIBRARY = Path(os.environ.get("LEAT_SAMPLER_LIBRARY") or Path(__file__).resolve(
 
 OK, E_ARGUMENT, E_CAPACITY, E_WORKSPACE, E_CUDA, E_DEVICE = 0, -1, -2, -3, -4, -5
 STATUS_FALLBACK, STATUS_TRUNCATED, STATUS_INTERNAL = 1, 2, 4
-FLAG_DIVIDE, FLAG_NO_FALLBACK, FLAG_LOGITS_BF16, FLAG_LOGITS_F16 = 1, 2, 4, 8
+FLAG_DIVIDE, FLAG_NO_FALLBACK, FLAG_LOGITS_BF16, FLAG_LOGITS_F16, FLAG_CLEAR_STATUS = 1, 2, 4, 8, 16
 
 _ERRORS = {
     E_ARGUMENT: "bad argument (null pointer, shape or broadcast row count)",

@@ -221,6 +221,8 @@ __global__ void __launch_bounds__(SAMPLE_CHUNKS + 32) floor_kernel(const __grid_
   if (tid == 0) {
     P.list_floor[b] = floor_from_sample(rc, P.vocab, SAMPLE_CHUNKS * (SAMPLE_CHUNK_BYTES / 16) * T::PER_VEC, P.list_cap, sorted);
     P.list_count[b] = 0;
+    // every kernel that may OR into the status word runs after this grid has ended
+    if (b == 0 && (P.flags & 16u) && P.status) *P.status = 0;
   }
 }
 

@@ -236,6 +236,9 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
   const bool filtered = h->has_list && !h->tune_no_filter && vec == 4 && !P.seen && P.vocab >= kFilterMinVocab;
   // 16-bit logits are read by the filter path only (and, row by row, by the multi-pass routine)
   if (P.dtype != 0 && (!filtered || P.cand_count)) return LEAT_E_ARGUMENT;
+  // LEAT_FLAG_CLEAR_STATUS: floor_kernel clears the word on the filter path, a memset node otherwise
+  if ((P.flags & LEAT_FLAG_CLEAR_STATUS) && P.status && !filtered &&
+      cuda_failed(cudaMemsetAsync(P.status, 0, sizeof(int), stream), "cudaMemsetAsync")) return LEAT_E_CUDA;
   if (filtered) {
     P.list = reinterpret_cast<unsigned long long*>(h->ws + h->L.list);
     P.list_count = reinterpret_cast<int*>(h->ws + h->L.list_count);
@@ -393,7 +396,13 @@ int leat_sample(leat_sampler_t* h, const leat_sample_args* a, leat_stream_t stre
   KParams P;
   int rc = fill_params(h, a, P);
   if (rc != LEAT_OK) return rc;
-  if (a->rows == 0) { h->launches = 0; return LEAT_OK; }
+  if (a->rows == 0) {
+    h->launches = 0;
+    if ((a->flags & LEAT_FLAG_CLEAR_STATUS) && a->status &&
+        cuda_failed(cudaMemsetAsync(a->status, 0, sizeof(int), static_cast<cudaStream_t>(stream)), "cudaMemsetAsync"))
+      return LEAT_E_CUDA;
+    return LEAT_OK;
+  }
   if (!a->out_ids) return LEAT_E_ARGUMENT;
   return launch_sample(h, P, static_cast<cudaStream_t>(stream));
 }
@@ -471,6 +480,8 @@ int finish_from(leat_sampler* h, const leat_sample_args* a, const float* cand_va
   P.g_value = cand_value; P.g_id = cand_id; P.g_count = cand_count;
   P.g_best = reinterpret_cast<const unsigned long long*>(best); P.g_parts = parts; P.cand_cap = cap;
   P.g_stride_value = stride_value; P.g_stride_id = stride_id; P.g_stride_count = stride_count; P.g_stride_best = stride_best;
+  if ((P.flags & LEAT_FLAG_CLEAR_STATUS) && P.status &&
+      cuda_failed(cudaMemsetAsync(P.status, 0, sizeof(int), stream), "cudaMemsetAsync")) return LEAT_E_CUDA;
   const int threads = 512;
   const int shared = (int)shared_bytes(h->cap, h->keep, 0, 0);
   finish_candidates_kernel<<<P.rows, threads, shared, stream>>>(P);

@@ -218,7 +218,8 @@ __device__ inline RowIn row_inputs_warp(const KParams& P, int b, const void* ext
   } else if (lane == 11) {
     src = reinterpret_cast<const uint32_t*>(extra);
   }
-  const uint32_t w = src ? *src : 0u;
+  // (the extra word is another kernel's output: read past L1)
+  const uint32_t w = src ? (lane == 11 ? __ldcg(src) : *src) : 0u;
   uint32_t v[12];
 #pragma unroll
   for (int i = 0; i < 12; ++i) v[i] = __shfl_sync(FULL, w, i);

@@ -191,7 +191,7 @@ class Sampler:
                 raise ValueError("uniform must be (B,)")
             keep.append(uniform)
             a.uniform = uniform.data_ptr()
-        a.vocab_offset, a.vocab_total, a.flags = vocab_offset, vocab_total, flags
+        a.vocab_offset, a.vocab_total, a.flags = vocab_offset, vocab_total, flags | _lib.FLAG_CLEAR_STATUS
         return a, keep
 
     # ---- entry points ---------------------------------------------------------------------------
@@ -205,7 +205,7 @@ class Sampler:
                              uniform, flags)  # fmt: skip
         rows, dev = a.rows, logits.device
         ids = out if out is not None else torch.empty((rows, 1), dtype=torch.int32, device=dev)
-        result = Sampled(ids, status=torch.zeros(1, dtype=torch.int32, device=dev))
+        result = Sampled(ids, status=torch.empty(1, dtype=torch.int32, device=dev))  # cleared by the call (FLAG_CLEAR_STATUS)
         a.out_ids, a.status = ids.data_ptr(), result.status.data_ptr()
         if want_greedy:
             result.greedy = torch.empty(rows, dtype=torch.int32, device=dev)
@@ -282,7 +282,7 @@ def sample_static(logits: torch.Tensor, options, seed=None, position=0, seen=Non
                             uniform, flags)  # fmt: skip
     rows, dev = a.rows, logits.device
     ids = out if out is not None else torch.empty((rows, 1), dtype=torch.int32, device=dev)
-    result = Sampled(ids, status=torch.zeros(1, dtype=torch.int32, device=dev))
+    result = Sampled(ids, status=torch.empty(1, dtype=torch.int32, device=dev))  # cleared by the call (FLAG_CLEAR_STATUS)
     a.out_ids, a.status = ids.data_ptr(), result.status.data_ptr()
     if want_greedy:
         result.greedy = torch.empty(rows, dtype=torch.int32, device=dev)

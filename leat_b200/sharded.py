@@ -105,7 +105,7 @@ class ShardedSampler:
         a, keep = self.sampler._args(dummy, options, seed, position, None, None, None, None, uniform, flags)
         a.vocab, a.vocab_total = self.vocab, self.vocab
         ids = out if out is not None else torch.empty((rows, 1), dtype=torch.int32, device=d)
-        result = Sampled(ids, status=torch.zeros(1, dtype=torch.int32, device=d))
+        result = Sampled(ids, status=torch.empty(1, dtype=torch.int32, device=d))  # cleared by the call (FLAG_CLEAR_STATUS)
         result.greedy = torch.empty(rows, dtype=torch.int32, device=d)
         result.cut = torch.empty(rows, dtype=torch.float32, device=d)
         result.kept = torch.empty(rows, dtype=torch.int32, device=d)
