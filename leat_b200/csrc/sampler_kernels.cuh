@@ -1036,6 +1036,8 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
   const int b = blockIdx.y, slice = blockIdx.x;
   if (P.only_rows && P.only_rows[b] != -2) return;
+  // a row with a list needs its first block only: the others leave before they set anything up
+  if (P.list && slice > 0 && __ldcg(&P.list_floor[b]) < __uint_as_float(0x7F800000u)) return;
   int S = P.slices;
   PHASE_BEGIN();
   const int begin = slice * P.slice_len;
