@@ -85,8 +85,7 @@ size_t fixed_shared(int cap, int keep) {
   return (size_t)cap * 8 + (size_t)keep * 8 + (size_t)(BINS + 32) * 4 + SMEM_FIXED;
 }
 
-size_t shared_bytes(int cap, int keep, int bm_words, int ht_size, size_t ring = 0) {
-  (void)bm_words;
+size_t shared_bytes(int cap, int keep, int ht_size, size_t ring = 0) {
   // the hash keys, then one area shared by their counts, the ring and the scratch of the finish
   size_t keys = ((size_t)ht_size * 4 + 127) / 128 * 128;
   size_t counts = (size_t)ht_size * 8;  // counts and the tokens' logits
@@ -130,7 +129,7 @@ Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool
     if (stages > MAX_RING_STAGES) stages = MAX_RING_STAGES;
     if (stages >= 2) p.ring_stages = stages;
   }
-  p.shared = (int)shared_bytes(h->cap, h->keep, p.bm_words, p.ht_size, (size_t)p.ring_stages * p.threads * RING_PER_THREAD * 4);
+  p.shared = (int)shared_bytes(h->cap, h->keep, p.ht_size, (size_t)p.ring_stages * p.threads * RING_PER_THREAD * 4);
   // a row the single pass cannot settle is redone in place by the multi-pass routine, which lays
   // out the block's shared memory its own way
   const int redo = (int)(G_BINS * 12 + 384 + (size_t)p.ht_size * 8);
@@ -483,7 +482,7 @@ int finish_from(leat_sampler* h, const leat_sample_args* a, const float* cand_va
   if ((P.flags & LEAT_FLAG_CLEAR_STATUS) && P.status &&
       cuda_failed(cudaMemsetAsync(P.status, 0, sizeof(int), stream), "cudaMemsetAsync")) return LEAT_E_CUDA;
   const int threads = 512;
-  const int shared = (int)shared_bytes(h->cap, h->keep, 0, 0);
+  const int shared = (int)shared_bytes(h->cap, h->keep, 0);
   finish_candidates_kernel<<<P.rows, threads, shared, stream>>>(P);
   if (cuda_failed(cudaGetLastError(), "finish_candidates_kernel launch")) return LEAT_E_CUDA;
   h->launches = 1;
