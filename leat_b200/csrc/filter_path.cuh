@@ -3,8 +3,8 @@
 //
 // Three launches instead of one fused kernel doing everything per block:
 //
-//   floor_kernel   one block per row reads a spread-out sample of the row (256 chunks of 128 bytes,
-//                  32 KB) and takes a low order statistic of the chunks' maxima as the row's floor:
+//   floor_kernel   one block per row reads a spread-out sample of the row (256 chunks of 128 bytes
+//                  in 64 pieces of 512, 32 KB) and takes a low order statistic of the chunks' maxima as the row's floor:
 //                  a raw logit above which, with overwhelming probability, at least top_k logits of
 //                  the row lie, and not many more.
 //   filter_kernel  streams every logit exactly once with 128-bit loads and nothing else to do than
@@ -146,17 +146,20 @@ __device__ __forceinline__ float logit_at(const KParams& P, int b, int i) {
 }
 
 // The descending chunk maxima of a row's sample, by the first SAMPLE_CHUNKS threads of the calling
-// block (every thread of the block must call); `maxima` and `sorted` are SAMPLE_CHUNKS floats of
-// shared memory each.  Rows are 16-byte aligned whole vectors, at least 2 * SAMPLE_SIZE logits long
-// (so that the chunks do not overlap).
+// block (whole warps; every thread of the block must call); `runs` is SAMPLE_CHUNKS 8-byte words of
+// shared memory, `sorted` as many floats.  Rows are 16-byte aligned whole vectors, at least
+// 2 * SAMPLE_SIZE logits long (so that the chunks do not overlap).
 template <typename T>
-__device__ __forceinline__ void sample_maxima(const void* row, int V, int dtype, float* maxima, float* sorted) {
-  const int tid = threadIdx.x;
+__device__ __forceinline__ void sample_maxima(const void* row, int V, unsigned long long* runs, float* sorted) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  unsigned long long key = 0ull;
   if (tid < SAMPLE_CHUNKS) {
-    // chunk tid starts at a multiple of its own length near tid * V / 256
+    // four chunks in a row make a piece of 512 bytes; piece p starts at a multiple of its own
+    // length near p * V / 64
     constexpr int VECS = SAMPLE_CHUNK_BYTES / 16;
     constexpr long long CHUNK = VECS * T::PER_VEC;  // logits
-    const long long at = ((long long)tid * V / SAMPLE_CHUNKS) & ~(CHUNK - 1);
+    constexpr int PIECES = SAMPLE_CHUNKS / 4;
+    const long long at = (((long long)(tid >> 2) * V / PIECES) & ~(4 * CHUNK - 1)) + (tid & 3) * CHUNK;
     const uint4* src = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(row) + at * (16 / T::PER_VEC));
     uint4 x[VECS];
 #pragma unroll
@@ -164,20 +167,42 @@ __device__ __forceinline__ void sample_maxima(const void* row, int V, int dtype,
     float m = neg_inf();  // fmaxf drops NaNs
 #pragma unroll
     for (int u = 0; u < VECS; ++u) m = fmaxf(m, vec_max<T>(x[u]));
-    maxima[tid] = m;
+    // ordered like the candidates' keys: value first, the chunk's number breaking ties
+    key = make_key(m, (uint32_t)tid);
+    // every warp sorts its 32 maxima in registers (a bitonic network over shuffles) ...
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+      for (int j = k >> 1; j > 0; j >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(FULL, key, j);
+        const bool keep_max = ((lane & k) == 0) == ((lane & j) == 0);
+        const unsigned long long hi = key > other ? key : other, lo = key > other ? other : key;
+        key = keep_max ? hi : lo;
+      }
+    }
+    runs[tid] = key;
   }
-  (void)dtype;
   __syncthreads();
   if (tid < SAMPLE_CHUNKS) {
-    // descending order by counting: place = number of maxima ahead of this one
-    const float v = maxima[tid];
-    int place = 0;
-#pragma unroll 8
-    for (int j = 0; j < SAMPLE_CHUNKS; ++j) {
-      const float o = maxima[j];
-      place += (o > v) || (o == v && j < tid);
+    // ... and a maximum's place is its place in its run plus the maxima above it in the other runs
+    constexpr int RUNS = SAMPLE_CHUNKS / 32;
+    int place = lane;
+#pragma unroll
+    for (int r0 = 0; r0 < RUNS; r0 += 4) {
+      int pos[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int step = 16; step > 0; step >>= 1) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          if (runs[(r0 + q) * 32 + pos[q] + step - 1] > key) pos[q] += step;
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (pos[q] == 31 && runs[(r0 + q) * 32 + 31] > key) pos[q] = 32;
+        if (r0 + q != warp) place += pos[q];
+      }
     }
-    sorted[place] = v;
+    sorted[place] = key_value(key);
   }
   __syncthreads();
 }
@@ -206,7 +231,7 @@ __device__ __forceinline__ float floor_from_sample(const RowCfg& rc, int V, int 
 // One block of 256 + 32 threads per row.  Writes the row's floor and clears the row's list.
 template <typename T>
 __global__ void __launch_bounds__(SAMPLE_CHUNKS + 32) floor_kernel(const __grid_constant__ KParams P) {
-  __shared__ float maxima[SAMPLE_CHUNKS];
+  __shared__ unsigned long long runs[SAMPLE_CHUNKS];
   __shared__ float sorted[SAMPLE_CHUNKS];
   __shared__ RowCfg rc;
   const int b = blockIdx.x, tid = threadIdx.x;
@@ -217,7 +242,7 @@ __global__ void __launch_bounds__(SAMPLE_CHUNKS + 32) floor_kernel(const __grid_
     if (tid == SAMPLE_CHUNKS) rc = row_config_from(P, in);
   }
   const unsigned char* row = reinterpret_cast<const unsigned char*>(P.logits) + (size_t)b * P.row_stride * (16 / T::PER_VEC);
-  sample_maxima<T>(row, P.vocab, P.dtype, maxima, sorted);
+  sample_maxima<T>(row, P.vocab, runs, sorted);
   if (tid == 0) {
     P.list_floor[b] = floor_from_sample(rc, P.vocab, SAMPLE_CHUNKS * (SAMPLE_CHUNK_BYTES / 16) * T::PER_VEC, P.list_cap, sorted);
     P.list_count[b] = 0;

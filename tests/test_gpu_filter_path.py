@@ -13,7 +13,7 @@ from tests import helpers
 
 pytestmark = pytest.mark.gpu
 
-V = 65536  # the floor kernel samples 32 logits at every multiple of 256 here
+V = 65536  # the floor kernel samples 128 logits at every multiple of 1024 here
 
 
 @pytest.fixture(scope="module")
@@ -61,7 +61,7 @@ def _options(rows, temperature=0.8, top_k=40, top_p=0.9):
 
 def _sampled_positions():
     at = np.arange(V)
-    return (at % 256) < 32
+    return (at % 1024) < 128
 
 
 @pytest.mark.parametrize("mode", ["U", "G"])
@@ -146,8 +146,8 @@ def test_shards_whose_lists_fail_are_streamed_again(device, mode):
     logits = rng.standard_normal((rows, vocab)).astype(np.float32)
     at = np.arange(vocab)
     # shard 0: large logits where its sample never looks; shard 1: only where it does; 2 and 3 plain
-    logits[:, (at < V) & ((at % 256) >= 32)] += 6.0
-    hot = np.flatnonzero((at >= V) & (at < 2 * V) & ((at % 256) < 32))[::50]
+    logits[:, (at < V) & ((at % 1024) >= 128)] += 6.0
+    hot = np.flatnonzero((at >= V) & (at < 2 * V) & ((at % 1024) < 128))[::50]
     logits[:, hot] += 9.0
     options = _options(rows, top_k=60, top_p=0.98)
     options[1, 0] = 0.0
