@@ -79,7 +79,10 @@ struct Plan {
   int vec, threads, slices, slice_len, bm_words, ht_size, shared, ring_stages;
 };
 
-constexpr size_t kSharedPerBlockTarget = 112 * 1024;  // two blocks per SM
+#ifndef LEAT_SHARED_TARGET_KB
+#define LEAT_SHARED_TARGET_KB 112
+#endif
+constexpr size_t kSharedPerBlockTarget = LEAT_SHARED_TARGET_KB * 1024;  // two blocks per SM
 
 size_t fixed_shared(int cap, int keep) {
   return (size_t)cap * 8 + (size_t)keep * 8 + (size_t)(BINS + 32) * 4 + SMEM_FIXED;
@@ -129,7 +132,12 @@ Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool
     if (stages > MAX_RING_STAGES) stages = MAX_RING_STAGES;
     if (stages >= 2) p.ring_stages = stages;
   }
-  p.shared = (int)shared_bytes(h->cap, h->keep, p.ht_size, (size_t)p.ring_stages * p.threads * RING_PER_THREAD * 4);
+  // the area behind the hash keys holds the ring, or at least a bitmap over the vocabulary (what a
+  // listed row marks its history tokens in) when that is not large
+  size_t behind = (size_t)p.ring_stages * p.threads * RING_PER_THREAD * 4;
+  const size_t bitmap = has_history ? (size_t)(vocab + 31) / 32 * 4 : 0;
+  if (bitmap <= 48 * 1024 && behind < bitmap) behind = bitmap;
+  p.shared = (int)shared_bytes(h->cap, h->keep, p.ht_size, behind);
   // a row the single pass cannot settle is redone in place by the multi-pass routine, which lays
   // out the block's shared memory its own way
   const int redo = (int)(G_BINS * 12 + 384 + (size_t)p.ht_size * 8);
