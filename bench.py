@@ -87,6 +87,22 @@ class ClockSampler:
             self.proc.terminate()
             self.thread.join(timeout=2)
 
+    def keep_busy(self, step, seconds: float = 0.6, wanted: int = 3) -> None:
+        """The timed steps last milliseconds and nvidia-smi answers every 100 ms: the same steps go
+        on, untimed, until a few samples are in (or `seconds` are over, whichever comes last, at most
+        five times that), so that the clocks are seen under the load that was timed."""
+        import torch
+
+        start, i = time.perf_counter(), 0
+        while True:
+            for _ in range(16):
+                step(i)
+                i += 1
+            torch.cuda.synchronize()
+            spent = time.perf_counter() - start
+            if (spent >= seconds and len(self.rows) >= wanted) or spent >= 5 * seconds:
+                return
+
     def summary(self) -> dict:
         sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
         top = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
@@ -307,6 +323,7 @@ def run_single(args) -> None:
         steps = max(inner, args.steps // inner * inner)
         ms = time_graph(lambda i: dw.step(sampler, i), steps, args.warmup, inner)
         launches = sampler.last_launches * steps
+        clocks.keep_busy(lambda i: dw.step(sampler, i))
         # end to end: host logits in pinned memory, copied in every step; ids read back every step
         from leat_b200 import sample as public_sample
 
@@ -423,11 +440,16 @@ def run_sharded(args) -> None:
             graph_step(i)
         b.record()
         torch.cuda.synchronize()
+        ms = torch.tensor([a.elapsed_time(b) / steps], device=device)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        ms = float(ms.item())
+        # the timed steps last milliseconds and nvidia-smi answers every 100 ms: the same steps go on,
+        # untimed, for about 0.6 s (the same number on every rank: each holds a collective)
+        for i in range(min(50000, int(600.0 / max(ms, 1e-3)))):
+            graph_step(i)
+        torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
-    ms = torch.tensor([a.elapsed_time(b) / steps], device=device)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms = float(ms.item())
     # end to end: this rank's slice comes from pinned host memory every step, the ids go back
     host_slice = torch.as_tensor(np.ascontiguousarray(w.logits[:, start:stop])).pin_memory()
     host_ids = torch.empty((w.rows, 1), dtype=torch.int32).pin_memory()
@@ -465,7 +487,7 @@ def run_sharded(args) -> None:
                          "algorithmic_bytes_per_launch": w.logit_bytes // world},
             "e2e": {"value": w.rows / (ms_e2e * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": int(host_slice.numel() * 4) * world,
                     "d2h_bytes_per_step": w.rows * 4 * world},
-            "gpu_launches": 5 * steps, "clocks": clocks.summary(),  # floor, filter, candidates, second pass, finish "clocks": clocks.summary(),
+            "gpu_launches": 5 * steps, "clocks": clocks.summary(),  # floor, filter, candidates, second pass, finish
         }  # fmt: skip
         print(json.dumps(line), flush=True)
     del selects, finish
