@@ -2,14 +2,17 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-One step = one pass of the sampler over one batch of logits (one call of the library's
-leat_sample on resident inputs).  N = 1 runs the batched server decode step (16 rows, 151936
-tokens: per-row temperature, top-k 64, min-p, presence/frequency/repetition penalties over a
-1024-token history); the logits of successive steps come from a pool of buffers larger than L2, so
-every step reads HBM.  N > 1 (under torchrun) runs the vocabulary-sharded configuration (512 rows,
-201088 tokens split over the ranks, one all-gather of candidates per step).  The last line printed
-by rank 0 is one JSON object; `all_configs` in it holds the device-timed figures of every
-configuration at one GPU.
+One step = one pass of the sampler over one batch of logits.  Every N runs the same workload, the
+largest configuration: 512 rows x 201088 tokens (temperature 0.7, top-k 64, top-p 0.95, repetition
+1.1 over a 512-token history, one supplied uniform per row), whose logits (412 MB) are larger than
+L2, so every step reads HBM.  N = 1 is one call of the library's leat_sample on resident inputs;
+N > 1 (under torchrun, one process per GPU) splits the vocabulary into N contiguous slices, one
+per rank, with one exchange of candidates per step ("strong" scaling: the work is fixed).
+
+Exactly K steps are timed, each a replay of a captured CUDA graph, with a CUDA event after every
+step on the launching stream: `ms_per_step` is the timed region divided by K, `median_ms` and
+`p95_ms` come from the per-step events.  The last line printed by rank 0 is one JSON object; at
+N = 1 `all_configs` in it holds the device-timed figures of every configuration.
 
 --impl reference times the CPU restatement of leat's exact sampler (oracle/) on the host's cores
 for the same workload: leat itself needs tinygrad, which is not installed here, so its own code
@@ -36,11 +39,16 @@ sys.path.insert(0, str(ROOT))
 FALLBACK_HBM_GBS = 6650.0  # an earlier measurement on this pool, used when MEASURED_PEAKS.json is absent
 NORTH_STAR_HBM_GBS = 8000.0
 L2_BYTES = 126 << 20
-# DRAM bytes filter_kernel moved per algorithmic byte in the ncu capture summarised in
-# profiles/filter_path_c3_160rows.md: (dram__bytes_read.sum + dram__bytes_write.sum) / (B x V x 4)
-# = (167.79 + 3.37) MB / 167.77 MB on 160 rows of the large-batch configuration; traffic grows with
-# the rows and the vocabulary, so it is scaled to the launch being reported
+# DRAM bytes filter_kernel moves per algorithmic byte, from one ncu capture of three launches on 160
+# rows of the large-batch configuration: (dram__bytes_read.sum + dram__bytes_write.sum) / (B x V x 4)
+# = (167.80 + 3.90) MB / 167.77 MB.  Traffic grows with the rows and the vocabulary, so it is
+# scaled to the launch being reported.
 TRAFFIC_PER_ALGORITHMIC_BYTE = 1.02
+HEADLINE = 5  # the configuration every N runs
+CPU_SAMPLE_ROWS = 32  # rows of the headline workload the CPU arm times per step
+
+WORKLOAD_NAMES = {1: "c1_single_row", 2: "c2_server_step", 3: "c3_large_batch", 4: "c4_draft_verify", 5: "c5_vocab_sharded"}
+SHAPES_ROWS = {1: 1, 2: 16, 3: 256, 4: 72, 5: 512}
 
 
 def peak_hbm() -> tuple[float, str]:
@@ -51,6 +59,12 @@ def peak_hbm() -> tuple[float, str]:
         except (ValueError, KeyError):
             pass
     return FALLBACK_HBM_GBS, "fallback"
+
+
+def headline_config(world: int, vocab: int) -> dict:
+    """The `config` object of the JSON line: the same in both arms and at every N but for the split."""
+    return {"workload": WORKLOAD_NAMES[HEADLINE], "rows": SHAPES_ROWS[HEADLINE], "vocab": vocab,
+            "parallelism": f"vocab{world}", "draw": "supplied uniform"}  # fmt: skip
 
 
 # ---- clocks -------------------------------------------------------------------------------------
@@ -87,22 +101,6 @@ class ClockSampler:
             self.proc.terminate()
             self.thread.join(timeout=2)
 
-    def keep_busy(self, step, seconds: float = 0.6, wanted: int = 3) -> None:
-        """The timed steps last milliseconds and nvidia-smi answers every 100 ms: the same steps go
-        on, untimed, until a few samples are in (or `seconds` are over, whichever comes last, at most
-        five times that), so that the clocks are seen under the load that was timed."""
-        import torch
-
-        start, i = time.perf_counter(), 0
-        while True:
-            for _ in range(16):
-                step(i)
-                i += 1
-            torch.cuda.synchronize()
-            spent = time.perf_counter() - start
-            if (spent >= seconds and len(self.rows) >= wanted) or spent >= 5 * seconds:
-                return
-
     def summary(self) -> dict:
         sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
         top = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
@@ -111,6 +109,17 @@ class ClockSampler:
         busy = [x for x in sm if x > 0.5 * max(sm)] if sm else []
         return {"sm_mhz": float(np.median(busy)) if busy else None, "sm_max_mhz": max(top) if top else None,
                 "reasons": reasons, "samples": len(sm)}  # fmt: skip
+
+
+def keep_busy(step, ms_per_step: float, seconds: float = 0.6) -> None:
+    """The timed steps last milliseconds and nvidia-smi answers every 100 ms: the same steps go on,
+    untimed, for about `seconds`, so that the clocks are seen under the load that was timed.  The
+    number of steps depends only on the (rank-agreed) step time, so every rank runs as many."""
+    import torch
+
+    for i in range(min(50000, int(seconds * 1e3 / max(ms_per_step, 1e-3)))):
+        step(i)
+    torch.cuda.synchronize()
 
 
 # ---- CPU baseline (the oracle on the host's cores) ------------------------------------------------
@@ -145,14 +154,15 @@ def cpu_rows_per_second(w, mode: str, seconds: float, threads: int) -> tuple[flo
 
 
 def run_reference(args) -> None:
+    """The reference arm: the CPU restatement on all host threads, a step = one pass over a bounded
+    sample (CPU_SAMPLE_ROWS rows) of the headline workload; rows/s does not depend on how many rows
+    a pass holds (rows are independent), so the figure stands for the 512-row step."""
     from leat_b200 import workloads
 
-    rank = int(os.environ.get("RANK", 0))
-    if rank != 0:
+    if int(os.environ.get("RANK", 0)) != 0:
         return
-    config = 2 if int(os.environ.get("WORLD_SIZE", 1)) == 1 else 5
-    # a step is one pass over a bounded sample of the workload's rows
-    w = workloads.config2() if config == 2 else workloads.config5(rows=32)
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    w = workloads.CONFIGS[HEADLINE](rows=CPU_SAMPLE_ROWS)
     threads = os.cpu_count() or 1
     times = []
     with ThreadPoolExecutor(threads) as pool:
@@ -161,23 +171,21 @@ def run_reference(args) -> None:
             if step >= args.warmup:
                 times.append(seconds)
     value = w.rows / float(np.mean(times))
-    sample = f"{args.steps} steps of {w.rows} rows x {w.vocab} of {WORKLOAD_NAMES[config]}, one row per task on {threads} threads"
+    sample = (f"{args.steps} steps of {w.rows} rows x {w.vocab} of {WORKLOAD_NAMES[HEADLINE]}, one row per task on "
+              f"{threads} threads; ms_per_step is scaled from {w.rows} rows to {SHAPES_ROWS[HEADLINE]}")  # fmt: skip
     line = {
         "impl": "reference", "metric": "sampler rows/s", "value": value, "unit": "rows/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * SHAPES_ROWS[config] / value,
-        "higher_is_better": True, "scaling": "weak" if config == 2 else "strong", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD_NAMES[config], "rows": SHAPES_ROWS[config], "vocab": w.vocab, "draw": "supplied uniform"},
-        "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port", "sample": sample},
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * SHAPES_ROWS[HEADLINE] / value,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": headline_config(world, w.vocab),
+        "extrapolated_from_rows": w.rows,
+        "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port", "sample": sample,
+                         "extrapolated_from_rows": w.rows},
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "leat's own sampler needs tinygrad (not installed, no network): this is the NumPy restatement of "
                 "its exact path (LEAT_KERNELS=ref) on the host cores",
     }  # fmt: skip
     print(json.dumps(line), flush=True)
-
-
-WORKLOAD_NAMES = {1: "c1_single_row", 2: "c2_server_step", 3: "c3_large_batch", 4: "c4_draft_verify", 5: "c5_vocab_sharded"}
-SHAPES_ROWS = {1: 1, 2: 16, 3: 256, 4: 72, 5: 512}
 
 
 # ---- the GPU arm ---------------------------------------------------------------------------------
@@ -192,6 +200,8 @@ class DeviceWorkload:
         self.w, self.device = w, device
         self.logit_bytes = w.logit_bytes if dtype is None else w.logit_bytes // 2
         copies = int(min(max_copies, max(1, -(-min_pool_bytes // self.logit_bytes))))
+        if self.logit_bytes > L2_BYTES:
+            copies = 1  # one buffer is already larger than L2
         base = torch.as_tensor(w.logits).to(device)
         if dtype is not None:  # the lm_head's own 16-bit output, read as it is
             base = base.to(dtype)
@@ -202,66 +212,92 @@ class DeviceWorkload:
         self.seed = torch.as_tensor(w.seed.astype(np.int64)).to(device).to(torch.uint32)
         self.out = torch.empty((w.rows, 1), dtype=torch.int32, device=device)
         self.l2_note = ("logits pool of %d buffers (%.0f MB) cycled, larger than L2" % (copies, copies * self.logit_bytes / 1e6)
-                        if copies > 1 else "inputs larger than L2")  # fmt: skip
+                        if copies > 1 else "inputs larger than L2 (%.0f MB per step)" % (self.logit_bytes / 1e6))  # fmt: skip
 
     def step(self, sampler, i: int):
         return sampler.sample_full(self.pool[i % len(self.pool)], self.options, self.seed, self.position,
                                    history=self.history, penalties=self.penalties, uniform=self.uniform, out=self.out)  # fmt: skip
 
 
-def time_device(step, steps: int, warmup: int) -> float:
-    """Mean milliseconds per step over `steps` steps, CUDA events on the launching stream."""
+def capture(step, inner: int):
+    """A CUDA graph holding steps 0 .. inner - 1 (launch overhead of the host taken out, as in leat's
+    engine, which replays captured graphs)."""
     import torch
 
-    for i in range(warmup):
-        step(i)
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for i in range(steps):
-        step(warmup + i)
-    b.record()
-    torch.cuda.synchronize()
-    return a.elapsed_time(b) / steps
-
-
-def time_graph(step, steps: int, warmup: int, inner: int) -> float:
-    """Mean milliseconds per step with `inner` steps captured in one CUDA graph (launch overhead
-    of the host taken out, as in leat's engine, which replays captured graphs)."""
-    import torch
-
-    for i in range(max(warmup, 3)):
-        step(i)
-    torch.cuda.synchronize()
     graph, stream = torch.cuda.CUDAGraph(), torch.cuda.Stream()
     with torch.cuda.stream(stream):
         with torch.cuda.graph(graph, stream=stream):
             for i in range(inner):
                 step(i)
     torch.cuda.synchronize()
-    replays = max(1, steps // inner)
+    return graph
+
+
+def timed_replays(replay, count: int) -> tuple[float, list[float]]:
+    """`count` calls of replay(i) with a CUDA event after each on the current stream: milliseconds
+    of the whole region, and of each call."""
+    import torch
+
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(count + 1)]
+    torch.cuda.synchronize()
+    marks[0].record()
+    for i in range(count):
+        replay(i)
+        marks[i + 1].record()
+    torch.cuda.synchronize()
+    return marks[0].elapsed_time(marks[count]), [marks[i].elapsed_time(marks[i + 1]) for i in range(count)]
+
+
+def time_config(step, pool_len: int, warmup: int, min_steps: int = 200) -> dict:
+    """Device time per step of one configuration: graphs of one step per pool buffer, at least
+    `min_steps` steps and eight replays; median and 95th percentile over the replays."""
+    import torch
+
+    for i in range(max(warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    graph = capture(step, pool_len)
+    replays = max(8, -(-min_steps // pool_len))
     graph.replay()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(replays):
-        graph.replay()
-    b.record()
-    torch.cuda.synchronize()
-    return a.elapsed_time(b) / (replays * inner)
+    total, each = timed_replays(lambda i: graph.replay(), replays)
+    per_step = np.array(each) / pool_len
+    return {"mean_ms": total / (replays * pool_len), "median_ms": float(np.median(per_step)),
+            "p95_ms": float(np.percentile(per_step, 95)), "replays": replays, "steps_per_replay": pool_len}  # fmt: skip
 
 
 def kernel_milliseconds(sampler, dw, steps: int = 12) -> dict:
     """Median duration of each kernel of a step, from CUDA events the library records on the
-    launching stream around its launches (plain launches, one step per pool buffer)."""
+    launching stream around its launches (plain launches, one step per pool buffer).  The events
+    keep the launches apart, so the overlap a replayed step has between them is lost and the four
+    sum to more than a step."""
     sampler.time_kernels(True)
     rows = []
     for i in range(steps + 3):
         dw.step(sampler, i)
         rows.append(sampler.kernel_times())
     sampler.time_kernels(False)
-    floor_ms, filter_ms, finish_ms = np.median(np.array(rows[3:]), axis=0)
-    return {"floor_kernel": float(floor_ms), "filter_kernel": float(filter_ms), "sample_kernel": float(finish_ms)}
+    floor_ms, filter_ms, finish_ms, rest_ms = np.median(np.array(rows[3:]), axis=0)
+    return {"floor_kernel": float(floor_ms), "filter_kernel": float(filter_ms), "finish_list_kernel": float(finish_ms),
+            "sample_kernel": float(rest_ms)}  # fmt: skip
+
+
+def oracle_parity(w, ids, kept, cut, rows: int) -> dict:
+    """The first `rows` rows of a result against the CPU oracle, by the parity rules of the tests:
+    kept counts and cuts bit-exact, sampled ids identical unless the oracle marks the row as a
+    nucleus-boundary tie (a float comparison within 1e-5 relative of flipping)."""
+    from oracle import sampler_oracle as oracle
+
+    sel = slice(0, rows)
+    want = oracle.sample(w.logits[sel], w.options[sel], w.seed[sel], w.position[sel], history=w.history[sel],
+                         penalties=w.penalties[sel], uniform_draws=w.uniform[sel], order="block", survivors=False)  # fmt: skip
+    mismatch = fragile = 0
+    for b in range(rows):
+        same = ids[b] == want.ids[b, 0] and kept[b] == want.kept[b] and cut[b] == want.cut[b]
+        if not same and want.margin[b] < 1e-5:
+            fragile += 1
+        elif not same:
+            mismatch += 1
+    return {"oracle_rows": rows, "oracle_mismatch": mismatch, "oracle_fragile": fragile}
 
 
 def run_one(args) -> None:
@@ -277,56 +313,66 @@ def run_one(args) -> None:
     w = workloads.CONFIGS[args.workload](**kw)
     sampler = Sampler(max(w.rows, 8), w.vocab, 256, device)
     dw = DeviceWorkload(w, device, min_pool_bytes=0, max_copies=1)
-    ms = time_device(lambda i: dw.step(sampler, i), args.steps, args.warmup)
-    print(json.dumps({"workload": WORKLOAD_NAMES[args.workload], "rows": w.rows, "vocab": w.vocab, "ms_per_step": ms,
+    for i in range(args.warmup):
+        dw.step(sampler, i)
+    total, _ = timed_replays(lambda i: dw.step(sampler, i), args.steps)
+    print(json.dumps({"workload": WORKLOAD_NAMES[args.workload], "rows": w.rows, "vocab": w.vocab,
+                      "ms_per_step": total / args.steps,
                       "launch": dict(zip(("threads", "slices", "shared_bytes"),
                                          sampler.plan(w.rows, w.vocab, 0 if w.history is None else w.history.shape[1]))),
-                      "kernels_per_step": sampler.last_launches}), flush=True)
+                      "kernels_per_step": sampler.last_launches}), flush=True)  # fmt: skip
 
 
 def run_single(args) -> None:
     import torch
 
+    from leat_b200 import sample as public_sample
     from leat_b200 import workloads
     from leat_b200.sampler import Sampler
 
-    device = torch.device("cuda", 0)
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
     torch.cuda.set_device(device)
     peak, peak_kind = peak_hbm()
     sampler = Sampler(512, 262144, 256, device)
 
-    # every configuration, device-timed under graph replay (kernel figures)
+    # every configuration, device-timed under graph replay
     all_configs = {}
-    for number, dtype in ((1, None), (2, None), (3, None), (4, None), (5, None), (3, torch.bfloat16)):
+    headline = None
+    for number, dtype in ((1, None), (2, None), (3, None), (4, None), (3, torch.bfloat16), (5, None)):
         w = workloads.CONFIGS[number]()
         dw = DeviceWorkload(w, device, dtype=dtype)
-        ms = time_graph(lambda i, dw=dw: dw.step(sampler, i), steps=max(args.steps, 2 * len(dw.pool)),
-                        warmup=args.warmup, inner=len(dw.pool))  # fmt: skip
+        timing = time_config(lambda i, dw=dw: dw.step(sampler, i), len(dw.pool), args.warmup)
+        ms = timing["median_ms"]
         gbs = dw.logit_bytes / (ms * 1e-3) / 1e9
+        launches_per_step = sampler.last_launches
         kernels = kernel_milliseconds(sampler, dw)
         filter_gbs = dw.logit_bytes / (kernels["filter_kernel"] * 1e-3) / 1e9 if kernels["filter_kernel"] > 0 else None
         all_configs[WORKLOAD_NAMES[number] + ("" if dtype is None else "_bf16_logits")] = {
-            "rows": w.rows, "vocab": w.vocab, "us_per_step": round(ms * 1e3, 2), "rows_per_s": round(w.rows / (ms * 1e-3)),
+            "rows": w.rows, "vocab": w.vocab, "us_per_step": round(ms * 1e3, 2), "p95_us": round(timing["p95_ms"] * 1e3, 2),
+            "mean_us": round(timing["mean_ms"] * 1e3, 2), "replays": timing["replays"], "steps_per_replay": timing["steps_per_replay"],
+            "rows_per_s": round(w.rows / (ms * 1e-3)), "launches_per_step": launches_per_step,
             "hbm_gbs": round(gbs, 1), "frac_of_measured": round(gbs / peak, 4), "frac_of_8tbs": round(gbs / NORTH_STAR_HBM_GBS, 4),
-            "kernel_us": {k: round(v * 1e3, 2) for k, v in kernels.items()},
+            "kernel_us_apart": {k: round(v * 1e3, 2) for k, v in kernels.items()},
             "filter_kernel_gbs": None if filter_gbs is None else round(filter_gbs, 1),
             "filter_kernel_frac_of_measured": None if filter_gbs is None else round(filter_gbs / peak, 4),
         }  # fmt: skip
-        del dw
-        torch.cuda.empty_cache()
+        if number == HEADLINE:
+            headline = (w, dw, kernels, launches_per_step)  # stays resident for the timed region below
+        else:
+            del dw
+            torch.cuda.empty_cache()
 
-    # the headline workload: the batched server decode step
-    w = workloads.config2()
-    dw = DeviceWorkload(w, device)
-    with ClockSampler(0) as clocks:
-        inner = len(dw.pool)
-        steps = max(inner, args.steps // inner * inner)
-        ms = time_graph(lambda i: dw.step(sampler, i), steps, args.warmup, inner)
-        launches = sampler.last_launches * steps
-        clocks.keep_busy(lambda i: dw.step(sampler, i))
-        # end to end: host logits in pinned memory, copied in every step; ids read back every step
-        from leat_b200 import sample as public_sample
-
+    # the headline: exactly K steps of the largest configuration, one graph replay and one event each
+    w, dw, kernels, launches_per_step = headline
+    graphs = [capture(lambda i, j=j: dw.step(sampler, j), 1) for j in range(len(dw.pool))]
+    for i in range(args.warmup):
+        graphs[i % len(graphs)].replay()
+    with ClockSampler(device.index) as clocks:
+        total, each = timed_replays(lambda i: graphs[i % len(graphs)].replay(), args.steps)
+        ms = total / args.steps
+        keep_busy(lambda i: graphs[i % len(graphs)].replay(), ms)
+        # end to end through the public call: host logits in pinned memory, copied in every step;
+        # ids read back every step
         host_logits = torch.as_tensor(w.logits).pin_memory()
         host_ids = torch.empty((w.rows, 1), dtype=torch.int32).pin_memory()
         staging = torch.empty_like(dw.pool[0])
@@ -338,42 +384,48 @@ def run_single(args) -> None:
             host_ids.copy_(ids, non_blocking=True)
             torch.cuda.current_stream().synchronize()
 
-        ms_e2e = time_device(e2e_step, args.steps, args.warmup)
-        kernels = kernel_milliseconds(sampler, dw)
+        for i in range(3):
+            e2e_step(i)
+        e2e_total, _ = timed_replays(e2e_step, args.steps)
+        ms_e2e = e2e_total / args.steps
+    result = sampler.sample_full(dw.pool[0], dw.options, dw.seed, dw.position, history=dw.history, penalties=dw.penalties,
+                                 uniform=dw.uniform, want_cut=True)  # fmt: skip
+    torch.cuda.synchronize()
+    parity = oracle_parity(w, result.ids.cpu().numpy().ravel(), result.kept.cpu().numpy(), result.cut.cpu().numpy(),
+                           CPU_SAMPLE_ROWS)  # fmt: skip
+    parity.update({"rows": w.rows, "mismatch": parity["oracle_mismatch"], "fragile": parity["oracle_fragile"],
+                   "status_word": int(result.status.item())})  # fmt: skip
     value = w.rows / (ms * 1e-3)
-    # the kernel that moves the bytes is filter_kernel: every logit once
-    achieved = w.logit_bytes / (kernels["filter_kernel"] * 1e-3) / 1e9
-    step_achieved = w.logit_bytes / (ms * 1e-3) / 1e9
-    traffic = None if TRAFFIC_PER_ALGORITHMIC_BYTE is None else TRAFFIC_PER_ALGORITHMIC_BYTE * w.logit_bytes
-    large = all_configs[WORKLOAD_NAMES[3]]
-
+    achieved = w.logit_bytes / (ms * 1e-3) / 1e9  # the whole call: every launch of a step
+    filter_gbs = w.logit_bytes / (kernels["filter_kernel"] * 1e-3) / 1e9
     threads = os.cpu_count() or 1
-    cpu_value, cpu_sample = cpu_rows_per_second(w, "U", seconds=12.0, threads=threads)
+    cpu_value, cpu_sample = cpu_rows_per_second(workloads.CONFIGS[HEADLINE](rows=CPU_SAMPLE_ROWS), "U", seconds=12.0, threads=threads)
     line = {
-        "metric": "sampler rows/s", "value": value, "unit": "rows/s", "n_gpus": 1, "steps": steps,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD_NAMES[2], "rows": w.rows, "vocab": w.vocab, "draw": "supplied uniform",
-                   "l2": dw.l2_note,
-                   "timing": "CUDA events around replays of a CUDA graph that holds one step per pool buffer"},
+        "metric": "sampler rows/s", "value": value, "unit": "rows/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "median_ms": float(np.median(each)), "p95_ms": float(np.percentile(each, 95)),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": headline_config(1, w.vocab),
+        "notes": {"l2": dw.l2_note,
+                  "timing": "CUDA events on the launching stream: one before the K steps, one after each; every step is "
+                            "a replay of a CUDA graph holding one leat_sample call; ms_per_step = region / K"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": traffic, "peak_kind": peak_kind, "kernel": "filter_kernel",
-                     "algorithmic_bytes_per_launch": w.logit_bytes,
-                     "launch_us": kernels["filter_kernel"] * 1e3,
-                     "kernel_us": {k: v * 1e3 for k, v in kernels.items()},
-                     "whole_step": {"achieved": step_achieved, "frac": step_achieved / peak,
-                                    "note": "all three launches of a step under graph replay"},
-                     "large_batch": {"workload": WORKLOAD_NAMES[3], "rows": large["rows"], "vocab": large["vocab"],
-                                     "filter_kernel_gbs": large["filter_kernel_gbs"],
-                                     "filter_kernel_frac": large["filter_kernel_frac_of_measured"],
-                                     "whole_step_gbs": large["hbm_gbs"], "whole_step_frac": large["frac_of_measured"]}},
+                     "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE * w.logit_bytes, "peak_kind": peak_kind,
+                     "kernel": "the whole call: floor_kernel, filter_kernel, finish_list_kernel, sample_kernel",
+                     "algorithmic_bytes_per_launch": w.logit_bytes, "launch_us": ms * 1e3,
+                     "frac_of_8tbs": achieved / NORTH_STAR_HBM_GBS,
+                     "filter_kernel": {"achieved": filter_gbs, "frac": filter_gbs / peak, "launch_us": kernels["filter_kernel"] * 1e3,
+                                       "note": "the kernel that moves the bytes, timed apart from the others by events around "
+                                               "plain launches (see kernel_us_apart)"},
+                     "kernel_us_apart": {k: v * 1e3 for k, v in kernels.items()}},
         "cpu_baseline": {"value": cpu_value, "unit": "rows/s", "cores": threads, "kind": "port", "sample": cpu_sample},
         "e2e": {"value": w.rows / (ms_e2e * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": w.logit_bytes,
                 "d2h_bytes_per_step": w.rows * 4},
-        "gpu_launches": launches, "clocks": clocks.summary(), "all_configs": all_configs,
+        "parity": parity, "gpu_launches": launches_per_step * args.steps, "clocks": clocks.summary(), "all_configs": all_configs,
         "us_per_step_b1": all_configs[WORKLOAD_NAMES[1]]["us_per_step"],
     }  # fmt: skip
     print(json.dumps(line), flush=True)
+    if parity["mismatch"]:
+        sys.exit(3)
 
 
 def run_sharded(args) -> None:
@@ -381,6 +433,7 @@ def run_sharded(args) -> None:
     import torch.distributed as dist
 
     from leat_b200 import workloads
+    from leat_b200.sampler import Sampler
     from leat_b200.sharded import ShardedSampler
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -389,13 +442,14 @@ def run_sharded(args) -> None:
     torch.cuda.set_device(device)
     dist.init_process_group("nccl", device_id=device)
     peak, peak_kind = peak_hbm()
-    w = workloads.config5()
+    w = workloads.CONFIGS[HEADLINE]()
     sharded = ShardedSampler(w.rows, w.vocab, k_max=64, cap=128, device=device)
     start, stop = sharded.start, sharded.stop
     t = lambda x: None if x is None else torch.as_tensor(x).to(device)  # noqa: E731
-    copies = max(1, -(-2 * L2_BYTES // ((stop - start) * w.rows * 4)))
+    slice_bytes = (stop - start) * w.rows * 4
+    copies = 1 if slice_bytes > L2_BYTES else min(32, -(-2 * L2_BYTES // slice_bytes))
     base = torch.as_tensor(np.ascontiguousarray(w.logits[:, start:stop])).to(device)
-    pool = [base] + [base.clone() for _ in range(min(copies, 32) - 1)]
+    pool = [base] + [base.clone() for _ in range(copies - 1)]
     options, penalties, history, uniform, position = t(w.options), t(w.penalties), t(w.history), t(w.uniform), t(w.position)
     seed = torch.as_tensor(w.seed.astype(np.int64)).to(device).to(torch.uint32)
     out = torch.empty((w.rows, 1), dtype=torch.int32, device=device)
@@ -407,47 +461,18 @@ def run_sharded(args) -> None:
     for i in range(args.warmup):
         step(i)
     torch.cuda.synchronize()
-    # the two device steps are replayed from CUDA graphs (one select graph per pool buffer, one finish
-    # graph), as a serving engine that replays captured decode steps would run them; the all-gather
-    # between them is issued eagerly
-    side = torch.cuda.Stream()
-    selects, finish = [], torch.cuda.CUDAGraph()
-    with torch.cuda.stream(side):
-        for buffer in pool:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                sharded.select(buffer, options, seed, position, history, None, penalties, uniform)
-            selects.append(g)
-        with torch.cuda.graph(finish, stream=side):
-            sharded.finish(w.rows, options, seed, position, uniform, out=out)
-    torch.cuda.synchronize()
-
-    def graph_step(i):
-        selects[i % len(selects)].replay()
-        sharded.exchange(w.rows)
-        finish.replay()
-
+    replay, how = sharded.replayable(pool, options, seed, position, history, penalties, uniform, out)
     for i in range(3):
-        graph_step(i)
+        replay(i)
     torch.cuda.synchronize()
-    steps = args.steps
     dist.barrier()
     torch.cuda.synchronize()
     with ClockSampler(local) as clocks:
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for i in range(steps):
-            graph_step(i)
-        b.record()
-        torch.cuda.synchronize()
-        ms = torch.tensor([a.elapsed_time(b) / steps], device=device)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        ms = float(ms.item())
-        # the timed steps last milliseconds and nvidia-smi answers every 100 ms: the same steps go on,
-        # untimed, for about 0.6 s (the same number on every rank: each holds a collective)
-        for i in range(min(50000, int(600.0 / max(ms, 1e-3)))):
-            graph_step(i)
-        torch.cuda.synchronize()
+        total, each = timed_replays(replay, args.steps)
+        stats = torch.tensor([total / args.steps, float(np.median(each)), float(np.percentile(each, 95))], device=device)
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        ms, median_ms, p95_ms = (float(x) for x in stats.tolist())
+        keep_busy(replay, ms)
     dist.barrier()
     torch.cuda.synchronize()
     # end to end: this rank's slice comes from pinned host memory every step, the ids go back
@@ -464,36 +489,62 @@ def run_sharded(args) -> None:
         e2e_step(i)
     dist.barrier()
     torch.cuda.synchronize()
-    a.record()
-    for i in range(args.steps):
-        e2e_step(i)
-    b.record()
-    torch.cuda.synchronize()
-    ms_e2e = torch.tensor([a.elapsed_time(b) / args.steps], device=device)
+    e2e_total, _ = timed_replays(e2e_step, args.steps)
+    ms_e2e = torch.tensor([e2e_total / args.steps], device=device)
     dist.all_reduce(ms_e2e, op=dist.ReduceOp.MAX)
     ms_e2e = float(ms_e2e.item())
+
+    # parity, outside the timed regions: one more step on every rank (it holds the exchange); every
+    # rank's ids must be the same; rank 0 compares them with the one-GPU sampler on the whole logits
+    # (all rows: ids, survivor counts, cuts) and with the CPU oracle on the first rows
+    result = sharded.sample(pool[0], options, seed, position, history=history, penalties=penalties, uniform=uniform)
+    torch.cuda.synchronize()
+    everyone = [torch.empty_like(result.ids) for _ in range(world)]
+    dist.all_gather(everyone, result.ids.contiguous())
+    parity = None
     if rank == 0:
+        ids = result.ids.cpu().numpy().ravel()
+        kept, cut = result.kept.cpu().numpy(), result.cut.cpu().numpy()
+        differing_ranks = sum(int(not torch.equal(everyone[0], other)) for other in everyone[1:])
+        single = Sampler(w.rows, w.vocab, 64, device)
+        one = single.sample_full(torch.as_tensor(w.logits).to(device), options, seed, position, history=history,
+                                 penalties=penalties, uniform=uniform, want_cut=True)  # fmt: skip
+        torch.cuda.synchronize()
+        vs_one = int(np.count_nonzero((ids != one.ids.cpu().numpy().ravel()) | (kept != one.kept.cpu().numpy())
+                                      | (cut != one.cut.cpu().numpy())))  # fmt: skip
+        parity = oracle_parity(w, ids, kept, cut, CPU_SAMPLE_ROWS)
+        parity.update({"rows": w.rows, "ranks_differing": differing_ranks, "rows_differing_from_one_gpu": vs_one,
+                       "mismatch": parity["oracle_mismatch"] + vs_one + differing_ranks, "fragile": parity["oracle_fragile"],
+                       "status_word": int(result.status.item())})  # fmt: skip
+        del single, one
         achieved = w.logit_bytes / world / (ms * 1e-3) / 1e9  # per GPU: each reads its slice once
         line = {
             "metric": "sampler rows/s", "value": w.rows / (ms * 1e-3), "unit": "rows/s", "n_gpus": world,
-            "steps": steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD_NAMES[5], "rows": w.rows, "vocab": w.vocab, "parallelism": f"vocab{world}",
-                       "draw": "supplied uniform", "l2": f"logits pool of {len(pool)} buffers per rank cycled, larger than L2",
-                       "exchange": "one NCCL all-gather of packed (score, id, count, greedy) candidate records per step",
-                       "timing": "CUDA events around the timed steps; the two device steps replayed from CUDA graphs, the all-gather issued eagerly between them; max over ranks"},
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "median_ms": median_ms, "p95_ms": p95_ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": headline_config(world, w.vocab),
+            "notes": {"l2": f"logits pool of {len(pool)} buffers per rank cycled, larger than L2" if len(pool) > 1
+                      else "each rank's slice is larger than L2",
+                      "exchange": sharded.exchange_note,
+                      "timing": "CUDA events on the launching stream: one before the K steps, one after each; " + how +
+                                "; every figure is the max over ranks"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind, "kernel": "whole step per GPU (floor, filter, candidates, all-gather, finish) over its vocabulary slice",
-                         "algorithmic_bytes_per_launch": w.logit_bytes // world},
+                         "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "the whole step per GPU (floor, filter, candidates, exchange, finish) over its vocabulary slice",
+                         "algorithmic_bytes_per_launch": w.logit_bytes // world, "launch_us": ms * 1e3},
             "e2e": {"value": w.rows / (ms_e2e * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": int(host_slice.numel() * 4) * world,
                     "d2h_bytes_per_step": w.rows * 4 * world},
-            "gpu_launches": 5 * steps, "clocks": clocks.summary(),  # floor, filter, candidates, second pass, finish
+            "parity": parity, "gpu_launches": sharded.launches_per_step * args.steps, "clocks": clocks.summary(),
         }  # fmt: skip
         print(json.dumps(line), flush=True)
-    del selects, finish
+    bad = torch.tensor([int(bool(parity and parity["mismatch"]))], device=device)
+    dist.broadcast(bad, 0)
+    del replay
     torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()
+    if int(bad.item()):
+        sys.exit(3)
 
 
 def main() -> None:
@@ -507,6 +558,7 @@ def main() -> None:
     parser.add_argument("--rows", type=int, default=0, help="with --workload: fewer rows than the configuration has")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
+    args.steps = max(args.steps, 1)
     if args.workload:
         run_one(args)
     elif args.impl == "reference":

@@ -134,10 +134,12 @@ int leat_sampler_plan(const leat_sampler_t* handle, int32_t rows, int32_t vocab,
                       int32_t* threads, int32_t* slices, int32_t* shared_bytes);
 /* Number of kernels the last call on this handle launched (host counter). */
 int leat_sampler_last_launches(const leat_sampler_t* handle);
-/* Measurement aid.  While enabled, leat_sample records CUDA events on the caller's stream around
-   its launches (do not capture such calls in a CUDA graph); leat_sampler_kernel_times waits for
-   the last call and writes three durations in milliseconds: floor_kernel, filter_kernel and
-   sample_kernel (the first two are 0 when the filter path was not taken). */
+/* Measurement aid.  While enabled, the kernels of a call on this handle record, in the workspace,
+   when their first block began and their last block ended (the GPU's nanosecond timer), also inside
+   a captured CUDA graph.  leat_sampler_kernel_times waits for the device and writes eight offsets in
+   milliseconds from the first begin of the last call: begin and end of filter_kernel,
+   finish_list_kernel, sample_kernel and floor_kernel (-1, -1 for a kernel the call did not launch).  Kernels of
+   one call overlap (each is a programmatic dependent of the one before), which the offsets show. */
 int leat_sampler_time_kernels(leat_sampler_t* handle, int32_t enabled);
 int leat_sampler_kernel_times(leat_sampler_t* handle, float* milliseconds);
 /* Text of the last CUDA error seen by this library on this thread (host pointer, static). */

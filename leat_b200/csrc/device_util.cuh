@@ -72,4 +72,19 @@ __device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v)
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Measurement aid: with a stamps array (16 words, zeroed before the call) a kernel's blocks record
+// the earliest begin and the latest end of kernel `k` on the GPU's nanosecond timer.  Begins are kept
+// complemented, so that one atomicMax serves both and zero means "never ran".
+__device__ __forceinline__ unsigned long long global_nanoseconds() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void stamp_begin(unsigned long long* stamps, int k) {
+  if (stamps && threadIdx.x == 0) atomicMax(&stamps[2 * k], ~global_nanoseconds());
+}
+__device__ __forceinline__ void stamp_end(unsigned long long* stamps, int k) {
+  if (stamps && threadIdx.x == 0) atomicMax(&stamps[2 * k + 1], global_nanoseconds());
+}
+
 }  // namespace leat

@@ -3,21 +3,24 @@
 //
 // Three launches instead of one fused kernel doing everything per block:
 //
-//   floor_kernel   one block per row reads a spread-out sample of the row (256 chunks of 128 bytes
-//                  in 64 pieces of 512, 32 KB) and takes a low order statistic of the chunks' maxima as the row's floor:
-//                  a raw logit above which, with overwhelming probability, at least top_k logits of
-//                  the row lie, and not many more.
-//   filter_kernel  streams every logit exactly once with 128-bit loads and nothing else to do than
-//                  compare it with its row's floor; the few hundred logits per row at or above it
-//                  are appended, as (logit, index) pairs, to the row's list in the workspace.
-//   sample_kernel  (one block per row) builds the candidate buffer from the list and from the row's
-//                  history tokens instead of streaming, and finishes the row as always.
+//   filter_kernel       streams every logit exactly once with 128-bit loads and nothing else to do
+//                       than compare it with its row's floor; the few hundred logits per row at or
+//                       above it are appended, as (logit, index) pairs, to the row's list in the
+//                       workspace.  The floor is a raw logit above which, with overwhelming
+//                       probability, at least top_k logits of the row lie, and not many more: a low
+//                       order statistic of the maxima of a spread-out sample of the row (256 chunks
+//                       of 128 bytes in 64 pieces of 512, 32 KB), which every block works out for
+//                       itself when it comes to a new row (the sample's lines are the row's own, so
+//                       the stream finds them in L2).
+//   finish_list_kernel  (finish_list.cuh) one small block per row finishes the row from its list.
+//   sample_kernel       takes the rows the list finish does not (rows without a list stream their
+//                       logits here) and leaves at once when there are none.
 //
 // The floor is only a guess, so the finish checks it: the result stands if at least top_k
 // candidates score strictly above the floor's score and the cut lies strictly above it too (then no
 // logit the filter dropped could have been a survivor or changed the cut); greedy rows need their
-// best candidate at or above the floor.  A row that fails the check is flagged and redone by the
-// exact multi-pass kernel.
+// best candidate at or above the floor.  A row that fails the check is redone by the exact
+// multi-pass routine.
 #pragma once
 
 constexpr int SAMPLE_CHUNKS = 256;   // chunks of the sample, one per thread of floor_kernel
@@ -28,7 +31,25 @@ constexpr int FILTER_THREADS = 256;
 constexpr int FILTER_VECS = 8;       // 128-bit loads in flight per thread
 constexpr int FILTER_STAGE = 64;     // pairs a warp collects in shared memory between flushes
 
+constexpr int FL_SORT = 512;            // most candidates finish_list_kernel sorts
+constexpr int FL_MAX_K = FL_SORT - 64;  // the largest top_k it takes
+
 __device__ __forceinline__ float pos_inf() { return __uint_as_float(0x7F800000u); }
+
+// What the filter leaves per row for the blocks and kernels that follow, in one 64-bit word (so one
+// load or store moves it whole): the row's floor (float32 bits), whether the list finish takes the
+// row, and a mark that the word is this call's.  The kernels that take the rows clear the mark.
+constexpr unsigned long long INFO_LEAN = 1ull << 32, INFO_READY = 1ull << 33;
+__device__ __forceinline__ float info_floor(unsigned long long info) { return __uint_as_float((uint32_t)info); }
+
+// Does finish_list_kernel take this row?  (sample_kernel takes the others.)  Worked out once per
+// row, by the filter, and kept in the workspace as the row's flag.
+__device__ __forceinline__ bool lean_takes(const KParams& P, const RowCfg& rc, float floor_l) {
+  if (!P.lean || !(floor_l < pos_inf())) return false;
+  if (P.history && !rc.lowers) return false;  // history tokens must be fetched one by one
+  if (rc.mode == M_ARGMAX_L || rc.mode == M_SELECT_MINP) return true;
+  return rc.mode == M_SELECT_K && rc.k_eff <= FL_MAX_K;
+}
 
 // Which order statistic of the sample bounds the top k of the row from below.  x = k * sample / V
 // sample elements are expected among the row's top k; the number that really are is close to
@@ -228,27 +249,48 @@ __device__ __forceinline__ float floor_from_sample(const RowCfg& rc, int V, int 
   return floor_l;
 }
 
-// One block of 256 + 32 threads per row.  Writes the row's floor and clears the row's list.
+// The floor of row b for a block of SAMPLE_CHUNKS threads that comes to the row: taken from the
+// workspace if a block before it has left it there already, else worked out from the row's sample
+// (blocks that start on the same row together all do so, to the same value) and left there for the
+// blocks and kernels that follow.
 template <typename T>
-__global__ void __launch_bounds__(SAMPLE_CHUNKS + 32) floor_kernel(const __grid_constant__ KParams P) {
-  __shared__ unsigned long long runs[SAMPLE_CHUNKS];
-  __shared__ float sorted[SAMPLE_CHUNKS];
-  __shared__ RowCfg rc;
-  const int b = blockIdx.x, tid = threadIdx.x;
-  grid_launch_dependents();  // the filter's blocks may take their places; they wait for this grid to end
-  if (tid >= SAMPLE_CHUNKS) {  // a warp of its own fetches the row's options while the sample is on its way
+__device__ __forceinline__ float block_floor(const KParams& P, int b, unsigned long long* runs, float* sorted, RowCfg* rc,
+                                             unsigned long long* known, bool look = true) {
+  const int tid = threadIdx.x;
+  __syncthreads();  // every thread is done with the floor before (`rc` and `known` are about to change)
+  if (look) {
+    if (tid == 0) *known = __ldcg(&P.list_info[b]);
+    __syncthreads();
+    const unsigned long long have = *known;
+    if (have & INFO_READY) return info_floor(have);
+  }
+  if (tid < 32) {
     uint32_t unused;
     const RowIn in = row_inputs_warp(P, b, nullptr, unused);
-    if (tid == SAMPLE_CHUNKS) rc = row_config_from(P, in);
+    if (tid == 0) *rc = row_config_from(P, in);
   }
   const unsigned char* row = reinterpret_cast<const unsigned char*>(P.logits) + (size_t)b * P.row_stride * (16 / T::PER_VEC);
   sample_maxima<T>(row, P.vocab, runs, sorted);
-  if (tid == 0) {
-    P.list_floor[b] = floor_from_sample(rc, P.vocab, SAMPLE_CHUNKS * (SAMPLE_CHUNK_BYTES / 16) * T::PER_VEC, P.list_cap, sorted);
-    P.list_count[b] = 0;
-    // every kernel that may OR into the status word runs after this grid has ended
-    if (b == 0 && (P.flags & 16u) && P.status) *P.status = 0;
-  }
+  const float floor_l = floor_from_sample(*rc, P.vocab, SAMPLE_CHUNKS * (SAMPLE_CHUNK_BYTES / 16) * T::PER_VEC, P.list_cap, sorted);
+  if (tid == 0)
+    P.list_info[b] = INFO_READY | (lean_takes(P, *rc, floor_l) ? INFO_LEAN : 0ull) | (unsigned long long)__float_as_uint(floor_l);
+  return floor_l;
+}
+
+// With few rows the floors are worked out ahead of the filter, one block per row, so that the many
+// blocks that then share a row find its floor waiting instead of each working it out.
+template <typename T>
+__global__ void __launch_bounds__(SAMPLE_CHUNKS) floor_kernel(const __grid_constant__ KParams P) {
+  __shared__ unsigned long long runs[SAMPLE_CHUNKS];
+  __shared__ float sorted[SAMPLE_CHUNKS];
+  __shared__ RowCfg rc;
+  __shared__ unsigned long long known;
+  grid_dependency_wait();  // (launched as a programmatic dependent of whatever wrote the logits)
+  stamp_begin(P.stamps, 3);
+  grid_launch_dependents();  // the filter's blocks may ask for their first logits meanwhile
+  if (blockIdx.x == 0 && threadIdx.x == 0 && (P.flags & 16u) && P.status) *P.status = 0;
+  block_floor<T>(P, blockIdx.x, runs, sorted, &rc, &known, false);
+  stamp_end(P.stamps, 3);
 }
 
 // A warp's finds on their way to a row's list: collected in shared memory (FILTER_STAGE pairs per
@@ -346,41 +388,100 @@ __device__ __forceinline__ void filter_process(const KParams& P, FilterStage& st
   st.held += total;
 }
 
+// 16 bytes global -> shared without passing through registers; waited for with async_wait_all()
+__device__ __forceinline__ void async_copy16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void async_wait_all() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
 // Streams the logits once.  A work item is FILTER_THREADS x FILTER_VECS consecutive vectors of one
-// row (8192 float32 logits or 16384 16-bit ones); the items are dealt to the blocks in contiguous
-// runs, so a block mostly stays within one row.
+// row (8192 float32 logits or 16384 16-bit ones).  With many rows the items are dealt to the blocks
+// in contiguous runs, so a block mostly stays within one row and needs one or two floors; with few
+// rows (`per` > 0) every row has `per` blocks of its own, which share its items, so that no block
+// ever changes rows.  When a block comes to a new row, the item's logits are on their way into
+// shared memory while the floor is found.
 template <typename T>
 __global__ void __launch_bounds__(FILTER_THREADS, 4) filter_kernel(const __grid_constant__ KParams P, int per_row,
-                                                                   int items) {
+                                                                   int items, int per, int floors_first) {
+  static_assert(FILTER_THREADS == SAMPLE_CHUNKS, "a block's threads take one chunk of the sample each");
+  extern __shared__ __align__(16) unsigned char filter_smem[];
+  uint4* ahead = reinterpret_cast<uint4*>(filter_smem);  // FILTER_THREADS x FILTER_VECS vectors
   __shared__ unsigned long long stage[FILTER_THREADS / 32][FILTER_STAGE];
+  __shared__ unsigned long long runs[SAMPLE_CHUNKS];
+  __shared__ float sorted[SAMPLE_CHUNKS];
+  __shared__ RowCfg rc;
+  __shared__ unsigned long long known;
   constexpr int SPAN = FILTER_THREADS * FILTER_VECS * T::PER_VEC;
   constexpr int BYTES = 16 / T::PER_VEC;
-  const int first = (int)((long long)blockIdx.x * items / gridDim.x);
-  const int last = (int)((long long)(blockIdx.x + 1) * items / gridDim.x);
+  int first = (int)((long long)blockIdx.x * items / gridDim.x);
+  int last = (int)((long long)(blockIdx.x + 1) * items / gridDim.x);
+  if (per > 0) {
+    const int r = blockIdx.x / per, j = blockIdx.x - r * per;
+    first = r * per_row + j * per_row / per;
+    last = r * per_row + (j + 1) * per_row / per;
+  }
   const unsigned char* logits = reinterpret_cast<const unsigned char*>(P.logits);
+  const int tid = threadIdx.x;
+  auto ask_ahead = [&](const unsigned char* row, int base) {
+#pragma unroll
+    for (int u = 0; u < FILTER_VECS; ++u) {
+      const int i = base + (u * FILTER_THREADS + tid) * T::PER_VEC;
+      if (i < P.vocab) async_copy16(&ahead[u * FILTER_THREADS + tid], row + (size_t)i * BYTES);
+    }
+  };
+  bool asked = false;
+  if (floors_first) {
+    // floor_kernel runs before this grid and waited for the logits itself: this block's first
+    // logits can be on their way while the floors are written
+    if (first < last) {
+      const int b = first / per_row;
+      ask_ahead(logits + (size_t)b * P.row_stride * BYTES, (first - b * per_row) * SPAN);
+      asked = true;
+    }
+    grid_dependency_wait();
+    stamp_begin(P.stamps, 0);
+  } else {
+    grid_dependency_wait();  // (launched as a programmatic dependent of whatever wrote the logits)
+    stamp_begin(P.stamps, 0);
+    // every kernel that may OR into the status word waits for this grid to end
+    if (blockIdx.x == 0 && tid == 0 && (P.flags & 16u) && P.status) *P.status = 0;
+  }
+  grid_launch_dependents();  // the blocks that finish rows may queue up behind this grid's
   FilterStage st;
-  st.mine = stage[threadIdx.x >> 5];
+  st.mine = stage[tid >> 5];
   st.held = 0;
   st.row = -1;
-  // the first item's logits are asked for before the floors are waited for: they are the caller's
-  uint4 x[FILTER_VECS];
-  if (first < last) {
-    const int b = first / per_row;
-    filter_load<T, FILTER_THREADS>(x, logits + (size_t)b * P.row_stride * BYTES, (first - b * per_row) * SPAN, P.vocab, P.dtype);
-  }
-  grid_dependency_wait();    // the floors are written
-  grid_launch_dependents();  // blocks that finish rows move in as this grid's blocks leave
+  float floor_l = pos_inf();
 #pragma unroll 1
   for (int item = first; item < last; ++item) {
     const int b = item / per_row;
     const int base = (item - b * per_row) * SPAN;
-    if (b != st.row) { filter_flush(P, st); st.row = b; }
-    const float floor_l = __ldcg(&P.list_floor[b]);
-    if (!(floor_l < pos_inf())) continue;  // the row does not use the list
-    if (item > first) filter_load<T, FILTER_THREADS>(x, logits + (size_t)b * P.row_stride * BYTES, base, P.vocab, P.dtype);
-    filter_process<T, FILTER_THREADS>(P, st, x, base, floor_l, logits + (size_t)b * P.row_stride * BYTES);
+    const unsigned char* row = logits + (size_t)b * P.row_stride * BYTES;
+    uint4 x[FILTER_VECS];
+    if (b != st.row) {
+      filter_flush(P, st);
+      st.row = b;
+      if (!asked) ask_ahead(row, base);
+      asked = false;
+      floor_l = block_floor<T>(P, b, runs, sorted, &rc, &known);
+      async_wait_all();  // (each thread reads back what it asked for itself)
+      if (!(floor_l < pos_inf())) continue;  // the row does not use the list
+#pragma unroll
+      for (int u = 0; u < FILTER_VECS; ++u) {
+        const int i = base + (u * FILTER_THREADS + tid) * T::PER_VEC;
+        x[u] = i < P.vocab ? ahead[u * FILTER_THREADS + tid] : minus_inf_vec(P.dtype);
+      }
+    } else {
+      if (!(floor_l < pos_inf())) continue;
+      filter_load<T, FILTER_THREADS>(x, row, base, P.vocab, P.dtype);
+    }
+    filter_process<T, FILTER_THREADS>(P, st, x, base, floor_l, row);
   }
   filter_flush(P, st);
+  stamp_end(P.stamps, 0);
 }
 
 // sample_kernel's replacement for the stream on a row that has a list: the listed logits become

@@ -34,7 +34,7 @@ int round_up(int x, int m) { return (x + m - 1) / m * m; }
 int next_pow2(int x) { int p = 1; while (p < x) p <<= 1; return p; }
 
 struct Layout {
-  size_t keys, count, best, vmin, ticket, flag, list, list_count, list_floor, total;
+  size_t keys, count, best, vmin, ticket, flag, list, list_count, list_info, stamps, total;
   int cells;
 };
 
@@ -51,7 +51,8 @@ Layout layout_for(int max_rows, int max_vocab, int keep) {
   L.flag = take((size_t)max_rows * 4);
   L.list = take((size_t)max_rows * kListCap * 8);
   L.list_count = take((size_t)max_rows * 4);
-  L.list_floor = take((size_t)max_rows * 4);
+  L.list_info = take((size_t)max_rows * 8);
+  L.stamps = take(16 * 8);
   L.total = at;
   return L;
 }
@@ -64,9 +65,10 @@ int cap_for(int keep) { return keep <= 512 ? 2048 : 4096; }
 struct leat_sampler {
   int device, max_rows, max_vocab, k_max, keep, cap;
   int tune_threads, tune_slices, tune_stages, tune_no_ring, tune_no_filter, has_list;
-  // optional per-kernel timing of a call: events around the floor, the filter and the finish
+  // optional per-kernel timing of a call: the kernels stamp their begin and end in the workspace
   int timing;
-  cudaEvent_t marks[4];
+  // a launch failed after lists were written: the next call empties the lists first
+  int dirty;
   int sm_count;
   int launches;
   unsigned char* ws;
@@ -77,12 +79,13 @@ namespace {
 
 struct Plan {
   int vec, threads, slices, slice_len, bm_words, ht_size, shared, ring_stages;
+  int grid_rows;  // blocks along the grid's row axis: 0 = one per row, else each takes several rows in turn
 };
 
-#ifndef LEAT_SHARED_TARGET_KB
-#define LEAT_SHARED_TARGET_KB 112
-#endif
-constexpr size_t kSharedPerBlockTarget = LEAT_SHARED_TARGET_KB * 1024;  // two blocks per SM
+constexpr int kMostShared = 200 * 1024;
+constexpr size_t kFilterAhead = (size_t)FILTER_THREADS * FILTER_VECS * 16;  // one work item, on its way in while a floor is found  // dynamic shared memory the kernels are allowed
+
+constexpr size_t kSharedPerBlockTarget = 112 * 1024;  // two blocks per SM
 
 size_t fixed_shared(int cap, int keep) {
   return (size_t)cap * 8 + (size_t)keep * 8 + (size_t)(BINS + 32) * 4 + SMEM_FIXED;
@@ -101,6 +104,7 @@ size_t shared_bytes(int cap, int keep, int ht_size, size_t ring = 0) {
 Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool has_history, int vec) {
   Plan p;
   p.vec = vec;
+  p.grid_rows = 0;
   p.threads = h->tune_threads ? h->tune_threads : 512;
   int step = p.threads * vec * UNROLL;
   int min_slices = (vocab + kMaxSliceLen - 1) / kMaxSliceLen;
@@ -145,6 +149,28 @@ Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool
   // words of the area behind the hash keys: room for a bitmap over the vocabulary
   p.bm_words = (int)((p.shared - fixed_shared(h->cap, h->keep) - ((size_t)p.ht_size * 4 + 127) / 128 * 128) / 4);
   return p;
+}
+
+// finish_list_kernel's dynamic shared memory for a call, or 0 when the call's history is too long for
+// it (then sample_kernel finishes listed rows too, as it does for shards).  ht: slots of its hash
+// table; area_words: words behind its keys.
+size_t lean_shared(int vocab, int history_cap, bool has_history, int old_ht_size, int* ht, int* area_words) {
+  size_t area = (size_t)FL_AREA_MIN_WORDS * 4;
+  *ht = 0;
+  if (has_history) {
+    *ht = next_pow2(history_cap * 2 < 64 ? 64 : history_cap * 2);
+    const size_t table = (size_t)*ht * 8;
+    if (table > 64 * 1024) return 0;
+    if (table > area) area = table;
+    const size_t bitmap = (size_t)(vocab + 31) / 32 * 4;
+    if (bitmap <= 32 * 1024 && bitmap > area) area = bitmap;
+  }
+  area = (area + 15) / 16 * 16;
+  *area_words = (int)(area / 4);
+  size_t total = FL_FIXED + (size_t)FL_HIST_WORDS * 4 + (size_t)FL_KEYS * 8 + area;
+  // a row the list cannot settle is redone in place by the multi-pass routine
+  const size_t redo = G_BINS * 12 + 384 + (size_t)old_ht_size * 8;
+  return total > redo ? total : redo;
 }
 
 bool aligned(const void* p, size_t a) { return ((uintptr_t)p % a) == 0; }
@@ -222,9 +248,10 @@ cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, s
 
 template <bool PEN>
 int launch_one(const KParams& P, const Plan& plan, cudaStream_t stream) {
-  dim3 grid(plan.slices, P.rows);
-  // after a filter launch the blocks may move in early; they wait before they read the lists
-  const cudaError_t e = P.list ? launch_dependent(sample_kernel<PEN>, grid, dim3(plan.threads), (size_t)plan.shared, stream, P)
+  dim3 grid(plan.slices, plan.grid_rows > 0 && plan.grid_rows < P.rows ? plan.grid_rows : P.rows);
+  // after the list finish the blocks may move in early (the filter's floors and flags are final by
+  // then); straight after a filter launch they must not
+  const cudaError_t e = (P.list && P.lean) ? launch_dependent(sample_kernel<PEN>, grid, dim3(plan.threads), (size_t)plan.shared, stream, P)
                                : (sample_kernel<PEN><<<grid, plan.threads, plan.shared, stream>>>(P), cudaGetLastError());
   return cuda_failed(e, "sample_kernel launch") ? LEAT_E_CUDA : LEAT_OK;
 }
@@ -243,39 +270,80 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
   const bool filtered = h->has_list && !h->tune_no_filter && vec == 4 && !P.seen && P.vocab >= kFilterMinVocab;
   // 16-bit logits are read by the filter path only (and, row by row, by the multi-pass routine)
   if (P.dtype != 0 && (!filtered || P.cand_count)) return LEAT_E_ARGUMENT;
-  // LEAT_FLAG_CLEAR_STATUS: floor_kernel clears the word on the filter path, a memset node otherwise
+  // LEAT_FLAG_CLEAR_STATUS: filter_kernel clears the word on the filter path, a memset node otherwise
   if ((P.flags & LEAT_FLAG_CLEAR_STATUS) && P.status && !filtered &&
       cuda_failed(cudaMemsetAsync(P.status, 0, sizeof(int), stream), "cudaMemsetAsync")) return LEAT_E_CUDA;
-  if (filtered) {
-    P.list = reinterpret_cast<unsigned long long*>(h->ws + h->L.list);
-    P.list_count = reinterpret_cast<int*>(h->ws + h->L.list_count);
-    P.list_floor = reinterpret_cast<float*>(h->ws + h->L.list_floor);
-    P.list_cap = kListCap;
-    if (h->timing) cudaEventRecord(h->marks[0], stream);
-    if (P.dtype == 0) floor_kernel<F32><<<P.rows, SAMPLE_CHUNKS + 32, 0, stream>>>(P);
-    else if (P.dtype == 1) floor_kernel<BF16><<<P.rows, SAMPLE_CHUNKS + 32, 0, stream>>>(P);
-    else floor_kernel<F16><<<P.rows, SAMPLE_CHUNKS + 32, 0, stream>>>(P);
-    if (cuda_failed(cudaGetLastError(), "floor_kernel launch")) return LEAT_E_CUDA;
-    if (h->timing) cudaEventRecord(h->marks[1], stream);
-    const int span = FILTER_THREADS * FILTER_VECS * (P.dtype == 0 ? 4 : 8);  // logits of one work item
-    const int per_row = (P.vocab + span - 1) / span;
-    const int items = per_row * P.rows;
-    const int blocks = items < h->sm_count * 4 ? items : h->sm_count * 4;  // four blocks fit an SM
-    const cudaError_t e =
-        P.dtype == 0 ? launch_dependent(filter_kernel<F32>, dim3(blocks), dim3(FILTER_THREADS), 0, stream, P, per_row, items)
-        : P.dtype == 1 ? launch_dependent(filter_kernel<BF16>, dim3(blocks), dim3(FILTER_THREADS), 0, stream, P, per_row, items)
-                       : launch_dependent(filter_kernel<F16>, dim3(blocks), dim3(FILTER_THREADS), 0, stream, P, per_row, items);
-    if (cuda_failed(e, "filter_kernel launch")) return LEAT_E_CUDA;
-    h->launches += 2;
+  if (h->timing) {
+    P.stamps = reinterpret_cast<unsigned long long*>(h->ws + h->L.stamps);
+    if (cuda_failed(cudaMemsetAsync(P.stamps, 0, 16 * 8, stream), "cudaMemsetAsync")) return LEAT_E_CUDA;
   }
-  if (h->timing) cudaEventRecord(h->marks[2], stream);
-  if (h->timing && !filtered) { cudaEventRecord(h->marks[0], stream); cudaEventRecord(h->marks[1], stream); }
   Plan plan = make_plan(h, P.rows, P.vocab, P.history_cap, P.history != nullptr, vec);
   P.slices = plan.slices; P.slice_len = plan.slice_len; P.bm_words = plan.bm_words; P.ht_size = plan.ht_size;
   P.ring_stages = plan.ring_stages;  // 0 unless rows are 16-byte aligned multiples of four floats
+  if (plan.shared > kMostShared) return LEAT_E_CAPACITY;  // (a history this long with top_k this large)
+  if (filtered) {
+    P.list = reinterpret_cast<unsigned long long*>(h->ws + h->L.list);
+    P.list_count = reinterpret_cast<int*>(h->ws + h->L.list_count);
+    P.list_info = reinterpret_cast<unsigned long long*>(h->ws + h->L.list_info);
+    P.list_cap = kListCap;
+    // the rows' lists are emptied by the kernels that take them; after a failed launch, here
+    if (h->dirty && (cuda_failed(cudaMemsetAsync(P.list_count, 0, (size_t)h->max_rows * 4, stream), "cudaMemsetAsync") ||
+                     cuda_failed(cudaMemsetAsync(P.list_info, 0, (size_t)h->max_rows * 8, stream), "cudaMemsetAsync")))
+      return LEAT_E_CUDA;
+    h->dirty = 1;
+    // one small block per row finishes the rows that have lists (not a shard's, which hands its
+    // candidates on); sample_kernel, after it, takes the rest
+    size_t lean_bytes = 0;
+    if (!P.cand_count) {
+      lean_bytes = lean_shared(P.vocab, P.history_cap, P.history != nullptr, plan.ht_size, &P.fl_ht, &P.fl_area_words);
+      if (lean_bytes > (size_t)kMostShared) lean_bytes = 0;
+    }
+    P.lean = lean_bytes > 0 ? 1 : 0;
+    const int span = FILTER_THREADS * FILTER_VECS * (P.dtype == 0 ? 4 : 8);  // logits of one work item
+    const int per_row = (P.vocab + span - 1) / span;
+    const int items = per_row * P.rows;
+    int blocks = items < h->sm_count * 4 ? items : h->sm_count * 4;  // four blocks fit an SM
+    // few rows: every row gets blocks of its own, so that no block works out more than one floor
+    int per = 0;
+    if (items > blocks && h->sm_count * 4 / P.rows >= 4) {
+      per = h->sm_count * 4 / P.rows;
+      if (per > per_row) per = per_row;
+      blocks = per * P.rows;
+    }
+    // few rows, but more than a handful: their floors are worked out first, one block per row,
+    // instead of by each of the many blocks that share a row (measured: 16 rows 16.8 against 19.8
+    // us per step, 72 rows 24.3 against 29.6; a single row 13.5 against 12.1)
+    const int floors_first = (P.rows >= 4 && (per > 0 || items <= blocks)) ? 1 : 0;
+    // the first launch is a programmatic dependent of whatever comes before it in the stream (the
+    // kernel that writes the logits): its blocks may be placed early, and wait before they read
+    if (floors_first) {
+      const cudaError_t e0 = P.dtype == 0   ? launch_dependent(floor_kernel<F32>, dim3(P.rows), dim3(SAMPLE_CHUNKS), 0, stream, P)
+                             : P.dtype == 1 ? launch_dependent(floor_kernel<BF16>, dim3(P.rows), dim3(SAMPLE_CHUNKS), 0, stream, P)
+                                            : launch_dependent(floor_kernel<F16>, dim3(P.rows), dim3(SAMPLE_CHUNKS), 0, stream, P);
+      if (cuda_failed(e0, "floor_kernel launch")) return LEAT_E_CUDA;
+      h->launches += 1;
+    }
+    const cudaError_t e =
+        P.dtype == 0 ? launch_dependent(filter_kernel<F32>, dim3(blocks), dim3(FILTER_THREADS), kFilterAhead, stream, P, per_row, items, per, floors_first)
+        : P.dtype == 1 ? launch_dependent(filter_kernel<BF16>, dim3(blocks), dim3(FILTER_THREADS), kFilterAhead, stream, P, per_row, items, per, floors_first)
+                       : launch_dependent(filter_kernel<F16>, dim3(blocks), dim3(FILTER_THREADS), kFilterAhead, stream, P, per_row, items, per, floors_first);
+    if (cuda_failed(e, "filter_kernel launch")) return LEAT_E_CUDA;
+    h->launches += 1;
+    if (P.lean) {
+      // twice the threads per row while every row's block still finds a place at once
+      const bool wide = P.rows <= h->sm_count * 2;
+      const cudaError_t e2 =
+          wide ? launch_dependent(finish_list_kernel<FL_THREADS_WIDE>, dim3(P.rows), dim3(FL_THREADS_WIDE), lean_bytes, stream, P)
+               : launch_dependent(finish_list_kernel<FL_THREADS>, dim3(P.rows), dim3(FL_THREADS), lean_bytes, stream, P);
+      if (cuda_failed(e2, "finish_list_kernel launch")) return LEAT_E_CUDA;
+      h->launches += 1;
+      // ... with a short grid of blocks that look at the rows' flags and mostly leave
+      const int resident = h->sm_count * 2;
+      plan.grid_rows = (resident + plan.slices - 1) / plan.slices;
+    }
+  }
   int rc = pen ? launch_one<true>(P, plan, stream) : launch_one<false>(P, plan, stream);
   if (rc != LEAT_OK) return rc;
-  if (h->timing) cudaEventRecord(h->marks[3], stream);
   h->launches += 1;
   if (filtered && P.cand_count) {
     // a shard's rows whose list did not hold up are streamed by a second launch; its blocks leave
@@ -286,6 +354,7 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
     if (rc != LEAT_OK) return rc;
     h->launches += 1;
   }
+  h->dirty = 0;
   return LEAT_OK;
 }
 
@@ -312,7 +381,7 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
   if (!h) return LEAT_E_ARGUMENT;
   h->device = device; h->max_rows = max_rows; h->max_vocab = max_vocab; h->k_max = k_max;
   h->keep = keep_for(k_max); h->cap = cap_for(h->keep);
-  h->tune_threads = 0; h->tune_slices = 0; h->tune_stages = 0; h->tune_no_ring = 0; h->tune_no_filter = 0; h->has_list = 1; h->timing = 0; h->launches = 0;
+  h->tune_threads = 0; h->tune_slices = 0; h->tune_stages = 0; h->tune_no_ring = 0; h->tune_no_filter = 0; h->has_list = 1; h->timing = 0; h->dirty = 0; h->launches = 0;
   h->L = layout_for(max_rows, max_vocab, h->keep);
   h->ws = static_cast<unsigned char*>(workspace);
   if (bytes < h->L.total || !aligned(workspace, 256)) { delete h; return LEAT_E_WORKSPACE; }
@@ -324,9 +393,10 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
     delete h; return LEAT_E_CUDA;
   }
   h->sm_count = sms > 0 ? sms : 148;
-  const int most = 200 * 1024;
+  const int most = kMostShared;
   if (allow_shared(sample_kernel<true>, most) || allow_shared(sample_kernel<false>, most) ||
-      allow_shared(finish_candidates_kernel, most)) {
+      allow_shared(finish_candidates_kernel, most) || allow_shared(finish_list_kernel<FL_THREADS>, most) ||
+      allow_shared(finish_list_kernel<FL_THREADS_WIDE>, most)) {
     delete h; return LEAT_E_CUDA;
   }
   if (cuda_failed(cudaMemset(workspace, 0, h->L.total), "cudaMemset") ||
@@ -338,7 +408,6 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
 }
 
 int leat_sampler_destroy(leat_sampler_t* handle) {
-  if (handle && handle->timing) leat_sampler_time_kernels(handle, 0);
   delete handle;
   return LEAT_OK;
 }
@@ -378,22 +447,24 @@ int leat_sampler_last_launches(const leat_sampler_t* h) { return h ? h->launches
 
 int leat_sampler_time_kernels(leat_sampler_t* h, int32_t enabled) {
   if (!h) return LEAT_E_ARGUMENT;
-  if (enabled && !h->timing) {
-    for (int i = 0; i < 4; ++i)
-      if (cuda_failed(cudaEventCreate(&h->marks[i]), "cudaEventCreate")) return LEAT_E_CUDA;
-  } else if (!enabled && h->timing) {
-    for (int i = 0; i < 4; ++i) cudaEventDestroy(h->marks[i]);
-  }
   h->timing = enabled ? 1 : 0;
   return LEAT_OK;
 }
 
 int leat_sampler_kernel_times(leat_sampler_t* h, float* milliseconds) {
   if (!h || !milliseconds || !h->timing) return LEAT_E_ARGUMENT;
-  if (cuda_failed(cudaEventSynchronize(h->marks[3]), "cudaEventSynchronize")) return LEAT_E_CUDA;
-  for (int i = 0; i < 3; ++i)
-    if (cuda_failed(cudaEventElapsedTime(&milliseconds[i], h->marks[i], h->marks[i + 1]), "cudaEventElapsedTime"))
-      return LEAT_E_CUDA;
+  unsigned long long stamps[16];
+  if (cuda_failed(cudaDeviceSynchronize(), "cudaDeviceSynchronize") ||
+      cuda_failed(cudaMemcpy(stamps, h->ws + h->L.stamps, sizeof(stamps), cudaMemcpyDeviceToHost), "cudaMemcpy"))
+    return LEAT_E_CUDA;
+  unsigned long long first = ~0ull;
+  for (int k = 0; k < 4; ++k)
+    if (stamps[2 * k] && ~stamps[2 * k] < first) first = ~stamps[2 * k];
+  for (int k = 0; k < 4; ++k) {
+    const bool ran = stamps[2 * k] != 0ull;
+    milliseconds[2 * k] = ran ? (float)((double)(~stamps[2 * k] - first) * 1e-6) : -1.0f;
+    milliseconds[2 * k + 1] = ran ? (float)((double)(stamps[2 * k + 1] - first) * 1e-6) : -1.0f;
+  }
   return LEAT_OK;
 }
 
@@ -580,7 +651,7 @@ int static_setup(int device, StaticDevice** out) {
     leat_sampler& h = sd.handle;
     h.device = device; h.max_rows = kStaticRows; h.max_vocab = kStaticVocab; h.k_max = kStaticK;
     h.keep = keep_for(kStaticK); h.cap = cap_for(h.keep);
-    h.tune_threads = 0; h.tune_slices = 0; h.tune_stages = 0; h.tune_no_ring = 0; h.tune_no_filter = 0; h.has_list = 0; h.timing = 0; h.launches = 0;
+    h.tune_threads = 0; h.tune_slices = 0; h.tune_stages = 0; h.tune_no_ring = 0; h.tune_no_filter = 0; h.has_list = 0; h.timing = 0; h.dirty = 0; h.launches = 0;
     Layout& L = h.L;
     L.cells = kStaticCells;
     size_t at = 0;
@@ -591,7 +662,7 @@ int static_setup(int device, StaticDevice** out) {
     L.vmin = take((size_t)L.cells * 4);
     L.ticket = take((size_t)kStaticRows * 4);
     L.flag = take((size_t)kStaticRows * 4);
-    L.list = 0; L.list_count = 0; L.list_floor = 0;  // the fixed scratch has no room for lists: the fused path is used
+    L.list = 0; L.list_count = 0; L.list_info = 0; L.stamps = 0;  // the fixed scratch has no room for lists: the fused path is used
     L.total = at;
     if (L.total > kStaticBytes || h.keep != kStaticKeep) return LEAT_E_WORKSPACE;
     h.ws = static_cast<unsigned char*>(scratch);
@@ -599,7 +670,7 @@ int static_setup(int device, StaticDevice** out) {
     if (cuda_failed(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute"))
       return LEAT_E_CUDA;
     h.sm_count = sms > 0 ? sms : 148;
-    const int most = 200 * 1024;
+    const int most = kMostShared;
     if (allow_shared(sample_kernel<true>, most) || allow_shared(sample_kernel<false>, most))
       return LEAT_E_CUDA;
     sd.ready = true;
@@ -629,17 +700,5 @@ int leat_sample_static(const leat_sample_args* a, leat_stream_t stream) {
     return LEAT_E_CUDA;
   return launch_sample(h, P, s);
 }
-
-#ifdef LEAT_PHASE_CLOCKS
-// development build only: cycles spent per phase, summed over blocks; clear != 0 zeroes them
-int leat_debug_phases(unsigned long long* out, int clear) {
-  if (out && cudaMemcpyFromSymbol(out, g_phase_cycles, sizeof(unsigned long long) * 32) != cudaSuccess) return -1;
-  if (clear) {
-    unsigned long long zero[32] = {0};
-    if (cudaMemcpyToSymbol(g_phase_cycles, zero, sizeof(zero)) != cudaSuccess) return -1;
-  }
-  return 0;
-}
-#endif
 
 }  // extern "C"

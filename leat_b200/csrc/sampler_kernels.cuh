@@ -25,25 +25,6 @@
 
 namespace leat {
 
-#ifdef LEAT_PHASE_CLOCKS
-__device__ unsigned long long g_phase_cycles[32];
-#define RB_MARK(i) do { if (threadIdx.x == 0) { long long now_ = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(now_ - rb_t0_)); rb_t0_ = now_; } } while (0)
-#define RB_BEGIN() long long rb_t0_ = clock64()
-#define RB_ADD1(i) atomicAdd(&g_phase_cycles[i], 1ull)
-#define FIN_MARK(i) do { __syncthreads(); RB_MARK(i); } while (0)
-#define SETUP_MARK(i) do { if (threadIdx.x == 0) atomicAdd(&g_phase_cycles[i], (unsigned long long)(clock64() - phase_t0_)); } while (0)
-#define PHASE_MARK(i) do { __syncthreads(); if (threadIdx.x == 0) { long long now_ = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(now_ - phase_t0_)); phase_t0_ = now_; } } while (0)
-#define PHASE_BEGIN() long long phase_t0_ = clock64()
-#else
-#define PHASE_MARK(i) do { } while (0)
-#define PHASE_BEGIN() do { } while (0)
-#define RB_MARK(i) do { } while (0)
-#define RB_BEGIN() do { } while (0)
-#define RB_ADD1(i) do { } while (0)
-#define FIN_MARK(i) do { } while (0)
-#define SETUP_MARK(i) do { } while (0)
-#endif
-
 enum RowMode : int {
   M_ARGMAX_L = 0,     // greedy: first argmax of the penalised logits
   M_ARGMAX_G = 1,     // no cut set, hashed draw: first argmax of score + gumbel over the whole row
@@ -89,9 +70,15 @@ struct KParams {
   unsigned* ws_ticket;          // (rows)
   int* ws_flag;                 // (rows): 1 = the row needs the multi-pass kernel
   // the filter path: per row a floor, and the list of (logit, index) pairs at or above it
-  unsigned long long* list; int* list_count; float* list_floor; int list_cap;
+  unsigned long long* list; int* list_count; int list_cap;
+  unsigned long long* list_info;  // (rows): floor, flag and mark of the row (filter_path.cuh)
   // a second pass over the rows a shard's list could not settle: only rows with only_rows[b] == -2
   const int* only_rows;
+  // finish_list_kernel runs before sample_kernel and takes the rows lean_takes() names; words of
+  // its area behind the keys, slots of its hash table of history tokens
+  int lean; int fl_area_words; int fl_ht;
+  // measurement aid (device_util.cuh: stamp_begin / stamp_end), or null
+  unsigned long long* stamps;
 };
 
 struct RowCfg {
@@ -310,7 +297,6 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
   unsigned long long* buf = c.buf;
   unsigned* hist = c.hist;
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, nwarps = nt >> 5;
-  RB_BEGIN();
   const int region = c.region;
   const int conv = sm.conv;
   const int n = (raw & 1) ? c.keep + nwarps * region : min(sm.n, c.cap);
@@ -352,7 +338,6 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
     if (lane == 0 && live) { atomicMax(&sm.vmax, mx); atomicMin(&sm.vmin, mn); atomicAdd(&sm.valid, live); }
   }
   __syncthreads();
-  RB_MARK(16);
   const int live = sm.valid;
   uint32_t lo = sm.vmin, hi = sm.vmax;  // the k-th largest lies in [lo, hi]
   uint32_t thr = 1u;                    // keep every live entry (key bits of any score exceed 0)
@@ -386,7 +371,6 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
         if (key && v >= lo && v <= hi) atomicAdd(&hist[bucket_of(v, low_v, scale, lo, shift)], 1u);
       }
       __syncthreads();
-      RB_MARK(18);
       // ---- C: the block walks the buckets from the top ----
       {
         unsigned* wtot = hist + BINS;
@@ -422,7 +406,6 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
         }
       }
       __syncthreads();
-      RB_MARK(19);
       chosen = sm.sel_bin;
       const unsigned at_or_above = above + (unsigned)sm.sel_above + (unsigned)sm.sel_count;
       const bool finest = scale == 0.0f && shift == 0;
@@ -457,8 +440,6 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
       if (tid == 0) { sm.rmin = 0xFFFFFFFFu; sm.rmax = 0u; }
     }
   }
-  RB_MARK(21);
-  if (threadIdx.x == 0) { RB_ADD1(24); }
   // ---- D: survivors go to the staging area; the smallest of them is the new threshold ----
   {
     uint32_t mn = 0xFFFFFFFFu;
@@ -477,7 +458,6 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
     if (by_bucket && lane == 0) atomicMin(&sm.smin2, mn);
   }
   __syncthreads();
-  RB_MARK(22);
   // ---- E: back to the front of the buffer ----
   const int m = min(sm.m, c.keep);
   if (by_bucket) thr = sm.smin2;
@@ -496,7 +476,6 @@ __device__ __noinline__ void buffer_rebuild(const Ctx& c, int raw) {
     sm.vmin = 0xFFFFFFFFu; sm.vmax = 0u; sm.m = 0; sm.valid = 0; sm.smin2 = 0xFFFFFFFFu;
   }
   __syncthreads();
-  RB_MARK(23);
 }
 
 // Block-synchronous append of one optional entry per thread (the merge of a row's slices).
@@ -559,20 +538,22 @@ __device__ inline void finish_simple(const KParams& P, int b, int mode, unsigned
   if (mode == M_ARGMAX_G && P.out_probs && P.status) atomicOr(P.status, 2);
 }
 
-// buf[0..sm.n) holds the row's candidates (unsorted).  Computes the cut and the draw and writes the
-// row's outputs.  fw / fi / fs are float scratch of cap, cap and cap/32 entries.
+// buf[0..sm.n) holds the row's candidates (unsorted, or likeliest first with `presorted`).  Computes
+// the cut and the draw and writes the row's outputs.  fw / fi / fs are float scratch of n, n and
+// 2 * ceil(n / 32) entries.
 __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, unsigned long long* buf,
                                   Shared& sm, float* fw, float* fi, float* fs, float row_min,
-                                  bool listed = false, float s_floor = 0.0f) {
+                                  bool listed = false, float s_floor = 0.0f, bool presorted = false) {
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
   const int n = sm.n;
-  RB_BEGIN();
   if (n <= 0) {  // nothing comparable in the row (all NaN)
     finish_simple(P, b, rc.mode, 0ull, 0ull, true);
     return;
   }
   if (tid == 0) { sm.jstar = 0; sm.ns = 0; sm.pick = NO_ID; sm.best = 0ull; sm.nstrict = 0; sm.redo = 0; }
-  if (n <= nt) {
+  if (presorted) {
+    __syncthreads();
+  } else if (n <= nt) {
     // one key per thread: every warp sorts its 32 keys in registers, then a key's place is its place
     // in its own run plus, for every other run, the number of keys there above it (a binary search)
     unsigned long long* runs = buf + P.cap / 2;
@@ -637,7 +618,6 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
     __syncthreads();
     block_sort_desc(buf, p2);
   }
-  FIN_MARK(25);
   const float top = key_value(buf[0]);
   const int in_k = min(rc.k_eff, n);
   const int nseg = (n + 31) >> 5;
@@ -667,7 +647,6 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
 #pragma unroll 1
   for (int j = tid; j < n; j += nt) fi[j] = fs[nseg + (j >> 5)] + fi[j];
   __syncthreads();
-  FIN_MARK(26);
   const float kept = fi[in_k - 1];
   const float bound_p = rc.p * kept;
   {
@@ -682,7 +661,6 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
     if (lane == 0 && last > 0) atomicMax(&sm.jstar, last);
   }
   __syncthreads();
-  FIN_MARK(27);
   float base = (rc.p < 1.0f) ? key_value(buf[sm.jstar]) : key_value(buf[in_k - 1]);
   if (rc.mode == M_SELECT_MINP) base = row_min;  // k = 0: the k-th score is the row's last
   float cut = fmaxf(base, top + rc.logm);
@@ -694,7 +672,6 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
     if (listed && r > s_floor && (j + 1 == n || !(key_value(buf[j + 1]) > s_floor))) sm.nstrict = j + 1;
   }
   __syncthreads();
-  FIN_MARK(28);
   const int ns = max(sm.ns, 1);
   const float total = fi[ns - 1];
   if (P.uniform) {
@@ -718,7 +695,6 @@ __device__ inline void finish_row(const KParams& P, const RowCfg& rc, int b, uns
     if (lane == 0) atomicMax(&sm.best, best);
   }
   __syncthreads();
-  FIN_MARK(29);
   if (tid == 0) {
     int id;
     if (P.uniform) id = key_id(buf[min(sm.pick, ns - 1)]);
@@ -1010,12 +986,11 @@ static_assert(sizeof(Shared) <= 256 && sizeof(Ctx) <= 128 && sizeof(RowCfg) <= 1
 
 #include "general_kernel.cuh"
 
-#ifndef LEAT_MIN_BLOCKS
-#define LEAT_MIN_BLOCKS 2
-#endif
+#include "finish_list.cuh"
+
+// One (row, slice) of sample_kernel's work, by the whole block.
 template <bool PEN>
-__global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __grid_constant__ KParams P) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+__device__ __forceinline__ void sample_block(const KParams& P, const int b, const int slice, unsigned char* smem_raw) {
   const SmemMap M = smem_map(smem_raw, P.cap, P.keep);
   unsigned long long* buf = M.buf;
   Shared& sm = *M.sm;
@@ -1034,12 +1009,10 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   ring.stages = P.ring_stages;
 
   const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31;
-  const int b = blockIdx.y, slice = blockIdx.x;
   if (P.only_rows && P.only_rows[b] != -2) return;
   // a row with a list needs its first block only: the others leave before they set anything up
-  if (P.list && slice > 0 && __ldcg(&P.list_floor[b]) < __uint_as_float(0x7F800000u)) return;
+  if (P.list && slice > 0 && info_floor(__ldcg(&P.list_info[b])) < __uint_as_float(0x7F800000u)) return;
   int S = P.slices;
-  PHASE_BEGIN();
   const int begin = slice * P.slice_len;
   int end = min(P.vocab, begin + P.slice_len);
   const float* row = P.logits + (size_t)b * P.row_stride;
@@ -1064,7 +1037,7 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   float* hraw = reinterpret_cast<float*>(hcnt + P.ht_size);
   RowIn in;
   uint32_t floor_bits = 0x7F800000u;
-  if (tid < 32) in = row_inputs_warp(P, b, P.list ? P.list_floor + b : nullptr, floor_bits);
+  if (tid < 32) in = row_inputs_warp(P, b, P.list ? P.list_info + b : nullptr, floor_bits);  // (the word's low half: the floor)
   if (tid == 0) {
     rc = row_config_from(P, in);
     c.buf = buf; c.stage = M.stage; c.hist = M.hist; c.sm = M.sm;
@@ -1100,10 +1073,11 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     for (int i = tid; i < zero; i += nt) hcnt[i] = 0;
   }
   __syncthreads();
-  SETUP_MARK(8);
   const int mode = rc.mode;
   // a row whose logits the filter listed needs one block, which owns the whole row
   const bool listed = sm.floor_l < __uint_as_float(0x7F800000u);
+  if (P.lean && (__ldcg(&P.list_info[b]) & INFO_LEAN)) return;  // finish_list_kernel's row
+  if (P.list && !P.lean && slice == 0 && tid == 0) P.list_info[b] &= ~INFO_READY;  // (the list finish clears it otherwise)
   if (listed) {
     if (slice > 0) return;
     S = 1;
@@ -1168,7 +1142,6 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     __syncthreads();
   }
 
-  PHASE_MARK(0);
   // ---- stream the slice once ----
   Tracked t;
   t.gl = neg_inf(); t.gid = NO_ID; t.al = neg_inf(); t.aid = NO_ID;
@@ -1181,25 +1154,19 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     const int pre_count = __ldcg(&P.list_count[b]);
     const unsigned long long pre_pair = __ldcg(&P.list[(size_t)b * P.list_cap + tid]);
     list_ok = list_load<PEN>(P, rc, c, h, bitmap, b, t, pre_count, pre_pair);
-    PHASE_MARK(1);
     if (PEN && P.history && list_ok && !rc.lowers) slice_history<PEN>(P, rc, c, h, row, seen_row, begin, end, t);
-    PHASE_MARK(2);
+    __syncthreads();
+    if (tid == 0) P.list_count[b] = 0;  // the list is taken: empty for the next call's filter
   } else if (mode != M_GENERAL) {
     const bool select = mode == M_SELECT_K || mode == M_SELECT_MINP;
     int from = begin;
     if (select) from = slice_fill<PEN>(P, rc, c, h, row, seen_row, begin, end, t);
-    PHASE_MARK(1);
     if (PEN && P.history) slice_history<PEN>(P, rc, c, h, row, seen_row, from, end, t);
-    PHASE_MARK(2);
     if (ring.stages > 0) stream_ring<PEN>(P, rc, c, h, row, seen_row, from, end, t, ring);
     else stream_plain<PEN>(P, rc, c, h, row, seen_row, from, end, t);
-    PHASE_MARK(3);
   }
   __syncthreads();
 
-#ifdef LEAT_PHASE_CLOCKS
-  phase_t0_ = clock64();
-#endif
   // ---- reduce what the slice found ----
   if (rc.track) {
     unsigned long long g = (t.gid != NO_ID) ? make_key(t.gl, (uint32_t)(t.gid + P.vocab_offset)) : 0ull;
@@ -1252,7 +1219,6 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     }
   }
 
-  PHASE_MARK(4);
   // ---- publish, and let the last block of the row go on ----
   if (S > 1) {
     const size_t cell = (size_t)b * S + slice;
@@ -1278,7 +1244,6 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     __syncthreads();
     if (!sm.is_last) return;
     __threadfence();
-    PHASE_MARK(5);
     // merge the row's slices
     if (tid == 0) { sm.n = 0; sm.conv = 0; sm.tau = neg_inf(); sm.overflow = 0; sm.smin = 0xFFFFFFFFu; }
     __syncthreads();
@@ -1364,7 +1329,6 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
   }
   __syncthreads();
 
-  PHASE_MARK(6);
   // ---- the row is whole in this block ----
   if (P.cand_count) {  // shard mode: hand the row's candidates to the gather
     const int cap = P.cand_cap;
@@ -1403,12 +1367,39 @@ __global__ void __launch_bounds__(512, LEAT_MIN_BLOCKS) sample_kernel(const __gr
     return;
   }
   finish_row(P, rc, b, buf, sm, fw, fi, fs, listed ? neg_inf() : unord32(sm.smin), listed, sm.s_floor);
-  PHASE_MARK(7);
   __syncthreads();
   if (sm.redo) {
     __syncthreads();
     general_row<PEN>(P, b, smem_raw);
   }
+}
+
+// The grid is (slices, rows) or, with fewer blocks along y than rows, each block takes every
+// gridDim.y-th row in turn (after finish_list_kernel most rows need nothing here, and a short grid
+// of blocks that look and leave costs less than one block per row).
+template <bool PEN>
+__global__ void __launch_bounds__(512, 2) sample_kernel(const __grid_constant__ KParams P) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  stamp_begin(P.stamps, 2);
+  if (P.lean) {
+    // after the list finish most calls leave nothing to do here: the filter's flags say so
+    int any = 0;
+#pragma unroll 1
+    for (int i = threadIdx.x; i < P.rows; i += blockDim.x) any |= (__ldcg(&P.list_info[i]) & INFO_LEAN) == 0ull;
+    if (!__syncthreads_or(any)) {
+      // this grid must not be over before the list finish is: what follows it in the stream may
+      // depend on this grid alone
+      grid_dependency_wait();
+      stamp_end(P.stamps, 2);
+      return;
+    }
+  }
+#pragma unroll 1
+  for (int b = blockIdx.y; b < P.rows; b += gridDim.y) {
+    sample_block<PEN>(P, b, blockIdx.x, smem_raw);
+    __syncthreads();
+  }
+  stamp_end(P.stamps, 2);
 }
 
 // Finishes rows from candidates gathered from `g_parts` vocabulary slices: one block per row.

@@ -49,20 +49,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint3
   return false;
 }
 
-#ifdef LEAT_PHASE_CLOCKS
-#define RING_CLOCK(x) long long x = clock64()
-#define RING_ADD(i, d) do { if (threadIdx.x == 0) atomicAdd(&g_phase_cycles[i], (unsigned long long)(d)); } while (0)
-#define RING_SET(x, y) x = y
-#else
-#define RING_CLOCK(x) do { } while (0)
-#define RING_ADD(i, d) do { } while (0)
-#define RING_SET(x, y) do { } while (0)
-#endif
-
-#ifndef LEAT_RING_PER_THREAD
-#define LEAT_RING_PER_THREAD 16
-#endif
-constexpr int RING_PER_THREAD = LEAT_RING_PER_THREAD;  // logits a thread takes from a stage
+constexpr int RING_PER_THREAD = 16;  // logits a thread takes from a stage
 
 struct Ring {
   float* data;              // stages x (threads x 16) floats
@@ -157,10 +144,8 @@ __device__ __noinline__ void stream_ring(const KParams& P, const RowCfg& rc, con
   int it = 0;
 #pragma unroll 1
   for (; it < steps && !stop; ++it) {
-    RING_CLOCK(a0);
     const int s = it % ring.stages;
     const bool landed = mbar_wait_bounded(&ring.bars[s], (uint32_t)(it / ring.stages) & 1u);
-    RING_CLOCK(a1);
     const int first = from + it * stage_elems + tid * 4;
     const float* stage = ring.data + (size_t)s * stage_elems;
     const float4* src = reinterpret_cast<const float4*>(stage) + tid;
@@ -272,10 +257,7 @@ __device__ __noinline__ void stream_ring(const KParams& P, const RowCfg& rc, con
       }
       // the step's barrier: every thread is done with the stage unless it has entries to redo;
       // did any warp run out of room, and did every copy land?
-      RING_CLOCK(a2);
       const int verdict = __syncthreads_or((redo != 0u ? 1 : 0) | (landed ? 0 : 2));
-      RING_CLOCK(a3);
-      RING_ADD(8, a1 - a0); RING_ADD(9, a2 - a1); RING_ADD(10, a3 - a2); RING_ADD(13, 1);
       if (verdict & 2) {  // a copy never landed: give the row up
         if (tid == 0) { sm.overflow = 1; if (P.status) atomicOr(P.status, 4); }
         stop = true;
@@ -283,9 +265,6 @@ __device__ __noinline__ void stream_ring(const KParams& P, const RowCfg& rc, con
       }
       if (!(verdict & 1)) break;
       buffer_rebuild(c, 1);
-      RING_CLOCK(a4);
-      RING_ADD(11, a4 - a3); RING_ADD(12, 1);
-      RING_SET(a1, a4);
       held = 0;
       floor_l = logit_floor(sm.tau, rc.tf);
       if (sm.overflow || ++rounds > 64) {

@@ -99,14 +99,17 @@ class Sampler:
         _lib.check(_lib.lib.leat_sampler_tune(self.handle, threads, slices), "leat_sampler_tune")
 
     def time_kernels(self, enabled: bool = True) -> None:
-        """Measurement aid: record CUDA events around the launches of each sample() (not under graph capture)."""
+        """Measurement aid: the kernels of each call stamp their begin and end (also under graph capture)."""
         _lib.check(_lib.lib.leat_sampler_time_kernels(self.handle, int(enabled)), "leat_sampler_time_kernels")
 
-    def kernel_times(self) -> tuple[float, float, float]:
-        """Milliseconds of floor_kernel, filter_kernel and sample_kernel in the last call (waits for it)."""
-        out = (_lib.C.c_float * 3)()
+    KERNELS = ("filter_kernel", "finish_list_kernel", "sample_kernel", "floor_kernel")
+
+    def kernel_times(self) -> dict[str, tuple[float, float]]:
+        """Begin and end of each kernel of the last call, milliseconds from the first begin (waits for
+        the device); kernels the call did not launch are left out."""
+        out = (_lib.C.c_float * 8)()
         _lib.check(_lib.lib.leat_sampler_kernel_times(self.handle, out), "leat_sampler_kernel_times")
-        return float(out[0]), float(out[1]), float(out[2])
+        return {name: (float(out[2 * k]), float(out[2 * k + 1])) for k, name in enumerate(self.KERNELS) if out[2 * k] >= 0}
 
     def tune_filter(self, enabled: bool = True) -> None:
         _lib.check(_lib.lib.leat_sampler_tune_filter(self.handle, int(enabled)), "leat_sampler_tune_filter")
