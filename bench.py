@@ -542,6 +542,7 @@ def run_sharded(args) -> None:
     del replay
     torch.cuda.synchronize()
     dist.barrier()
+    sharded.close()
     dist.destroy_process_group()
     if int(bad.item()):
         sys.exit(3)

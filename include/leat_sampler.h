@@ -24,6 +24,7 @@ extern "C" {
 #endif
 
 typedef struct leat_sampler leat_sampler_t;
+typedef struct leat_shard leat_shard_t;
 typedef void* leat_stream_t; /* a cudaStream_t */
 
 enum {
@@ -39,7 +40,8 @@ enum {
 enum {
   LEAT_STATUS_FALLBACK = 1,  /* a row took the exact multi-pass path (informational) */
   LEAT_STATUS_TRUNCATED = 2, /* a row had more survivors than out_width; probabilities clipped */
-  LEAT_STATUS_INTERNAL = 4   /* an internal bound was exceeded; the row's id is -1 */
+  LEAT_STATUS_INTERNAL = 4,  /* an internal bound was exceeded; the row's id is -1 */
+  LEAT_STATUS_PEER = 8       /* vocabulary shards: another rank's hand-over did not arrive within the wait's limit */
 };
 
 /* flags */
@@ -213,6 +215,42 @@ size_t leat_candidate_record_bytes(int32_t rows, int32_t cap);
 int leat_candidate_record_layout(int32_t rows, int32_t cap, size_t* id_at, size_t* count_at, size_t* best_at);
 int leat_sample_from_records(leat_sampler_t* handle, const leat_sample_args* args, const void* records,
                              int32_t parts, int32_t cap, leat_stream_t stream);
+
+/* Vocabulary shards that exchange candidates over peer memory instead of a collective (no reference
+   counterpart, like the entries above).  Every rank owns a slice of the vocabulary and a share of
+   the rows.  A step is three calls on every rank, on one stream, all ranks taking the same steps in
+   the same order:
+
+     leat_shard_select  filters the rank's slice (args as for leat_topk_local) and stores each row's
+                        candidates straight into the exchange region of the rank that owns the row
+     leat_shard_finish  finishes the rows this rank owns from every rank's candidates (waiting, with a
+                        limit, for their arrival) and stores the results into every rank's region
+     leat_shard_result  waits (with a limit) for every owner's results and writes them to args'
+                        out_ids, out_greedy, out_cut, out_kept (rows,), the same on every rank
+
+   args of the last two: rows, options, seed, position, uniform, flags as for the select; vocab (or
+   vocab_total) the whole vocabulary's size; logits ignored; out_probs is not supported.  Pass
+   LEAT_FLAG_CLEAR_STATUS to the select only.  A wait that runs out (a rank that never took the
+   step) ORs LEAT_STATUS_PEER | LEAT_STATUS_INTERNAL into the status word and the ids read -1; the
+   kernels end, nothing hangs.
+
+   Regions: leat_shard_region_bytes(rows, cap, world) bytes per rank, zeroed, each mapped into every
+   rank's address space: leat_peer_alloc makes one with cudaMalloc and returns its 64-byte
+   inter-process handle, leat_peer_open maps another process's (peer access is enabled as needed);
+   ranks in one process may pass plain pointers.  leat_shard_create takes the `world` region
+   pointers as this process sees them (index = rank); all ranks must have zeroed their regions
+   before any rank's first step.  Only stores cross NVLink; every rank reads its own region. */
+size_t leat_shard_region_bytes(int32_t rows, int32_t cap, int32_t world);
+int leat_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
+int leat_peer_open(const unsigned char* handle64, void** ptr);
+int leat_peer_close(void* ptr);
+int leat_peer_free(void* ptr);
+int leat_shard_create(leat_sampler_t* handle, int32_t rank, int32_t world, int32_t rows, int32_t cap,
+                      void* const* regions, leat_shard_t** out);
+int leat_shard_destroy(leat_shard_t* shard);
+int leat_shard_select(leat_shard_t* shard, const leat_sample_args* args, leat_stream_t stream);
+int leat_shard_finish(leat_shard_t* shard, const leat_sample_args* args, leat_stream_t stream);
+int leat_shard_result(leat_shard_t* shard, const leat_sample_args* args, leat_stream_t stream);
 
 #ifdef __cplusplus
 }

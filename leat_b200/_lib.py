@@ -11,7 +11,7 @@ from pathlib import Path
 LIBRARY = Path(os.environ.get("LEAT_SAMPLER_LIBRARY") or Path(__file__).resolve().parent / "csrc" / "libleat_sampler.so")
 
 OK, E_ARGUMENT, E_CAPACITY, E_WORKSPACE, E_CUDA, E_DEVICE = 0, -1, -2, -3, -4, -5
-STATUS_FALLBACK, STATUS_TRUNCATED, STATUS_INTERNAL = 1, 2, 4
+STATUS_FALLBACK, STATUS_TRUNCATED, STATUS_INTERNAL, STATUS_PEER = 1, 2, 4, 8
 FLAG_DIVIDE, FLAG_NO_FALLBACK, FLAG_LOGITS_BF16, FLAG_LOGITS_F16, FLAG_CLEAR_STATUS = 1, 2, 4, 8, 16
 
 _ERRORS = {
@@ -29,6 +29,8 @@ EXPORTS = [
     "leat_sampler_last_cuda_error", "leat_sample", "leat_argmax", "leat_cutoff",
     "leat_verify_draft", "leat_topk_local", "leat_sample_from_candidates", "leat_sample_static",
     "leat_candidate_record_bytes", "leat_candidate_record_layout", "leat_sample_from_records",
+    "leat_shard_region_bytes", "leat_peer_alloc", "leat_peer_open", "leat_peer_close", "leat_peer_free",
+    "leat_shard_create", "leat_shard_destroy", "leat_shard_select", "leat_shard_finish", "leat_shard_result",
 ]  # fmt: skip
 
 
@@ -87,9 +89,21 @@ def _load() -> C.CDLL:
     lib.leat_candidate_record_bytes.argtypes = [i32, i32]
     lib.leat_candidate_record_layout.argtypes = [i32, i32, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]
     lib.leat_sample_from_records.argtypes = [p, C.POINTER(SampleArgs), p, i32, i32, p]
+    lib.leat_shard_region_bytes.restype = sz
+    lib.leat_shard_region_bytes.argtypes = [i32, i32, i32]
+    lib.leat_peer_alloc.argtypes = [sz, C.POINTER(p), C.c_char_p]
+    lib.leat_peer_open.argtypes = [C.c_char_p, C.POINTER(p)]
+    lib.leat_peer_close.argtypes = [p]
+    lib.leat_peer_free.argtypes = [p]
+    lib.leat_shard_create.argtypes = [p, i32, i32, i32, i32, C.POINTER(p), C.POINTER(p)]
+    lib.leat_shard_destroy.argtypes = [p]
+    lib.leat_shard_select.argtypes = [p, C.POINTER(SampleArgs), p]
+    lib.leat_shard_finish.argtypes = [p, C.POINTER(SampleArgs), p]
+    lib.leat_shard_result.argtypes = [p, C.POINTER(SampleArgs), p]
     for name in EXPORTS:
         fn = getattr(lib, name)
-        if name not in ("leat_sampler_workspace_bytes", "leat_sampler_last_cuda_error", "leat_candidate_record_bytes"):
+        if name not in ("leat_sampler_workspace_bytes", "leat_sampler_last_cuda_error", "leat_candidate_record_bytes",
+                        "leat_shard_region_bytes"):
             fn.restype = C.c_int
     return lib
 

@@ -257,8 +257,23 @@ __device__ __forceinline__ int fl_count(const unsigned* hkeys, const unsigned* h
 // sorted[0..n) holds the row's candidates, likeliest first.  The cut and the draw, as finish_row
 // computes them (the same sums in the same order), with fewer barriers: a segment's offset is summed
 // by every thread that needs it instead of being handed round.  fw / fx hold n floats, fs n / 32.
-template <int NT>
-__device__ __forceinline__ void fl_finish(const KParams& P, const RowCfg& rc, int b, const unsigned long long* sorted,
+// where a finished row's results go (any but `id` may be null)
+struct RowOut {
+  int* id; float* cut; int* kept; float* probs; int* prob_ids; int width;
+};
+__device__ __forceinline__ RowOut row_out(const KParams& P, int b) {
+  RowOut o;
+  o.id = P.out_ids ? P.out_ids + b : nullptr;
+  o.cut = P.out_cut ? P.out_cut + b : nullptr;
+  o.kept = P.out_kept ? P.out_kept + b : nullptr;
+  o.probs = P.out_probs ? P.out_probs + (size_t)b * P.out_width : nullptr;
+  o.prob_ids = P.out_prob_ids ? P.out_prob_ids + (size_t)b * P.out_width : nullptr;
+  o.width = P.out_width;
+  return o;
+}
+
+template <int NT, bool CHECK>
+__device__ __forceinline__ void fl_finish(const KParams& P, const RowCfg& rc, const RowOut& out, const unsigned long long* sorted,
                                           int n, FLShared& S, float* fw, float* fx, float* fs, float s_floor) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float top = key_value(sorted[0]);
@@ -309,7 +324,7 @@ __device__ __forceinline__ void fl_finish(const KParams& P, const RowCfg& rc, in
     const float r = key_value(sorted[j]);
     const float next = j + 1 < n ? key_value(sorted[j + 1]) : neg_inf();
     if (r >= cut && (j + 1 == n || !(next >= cut))) S.ns = j + 1;
-    if (r > s_floor && (j + 1 == n || !(next > s_floor))) S.nstrict = j + 1;
+    if (CHECK && r > s_floor && (j + 1 == n || !(next > s_floor))) S.nstrict = j + 1;
   }
   __syncthreads();
   const int ns = max(S.ns, 1);
@@ -337,30 +352,35 @@ __device__ __forceinline__ void fl_finish(const KParams& P, const RowCfg& rc, in
   __syncthreads();
   if (tid == 0) {
     int id = P.uniform ? key_id(sorted[min(S.pick, ns - 1)]) : key_id(S.best);
-    // the list stands only if nothing the filter dropped could have mattered: enough candidates
-    // strictly above the floor's score, and the cut strictly above it
-    const bool enough = rc.mode == M_SELECT_MINP || S.nstrict >= rc.k_eff;
-    if (!(enough && cut > s_floor)) {
-      id = -1;
-      if (!(P.flags & 2u)) S.redo = 1;
-      else if (P.status) atomicOr(P.status, 4);
+    if (CHECK) {
+      // the list stands only if nothing the filter dropped could have mattered: enough candidates
+      // strictly above the floor's score, and the cut strictly above it
+      const bool enough = rc.mode == M_SELECT_MINP || S.nstrict >= rc.k_eff;
+      if (!(enough && cut > s_floor)) {
+        id = -1;
+        if (!(P.flags & 2u)) S.redo = 1;
+        else if (P.status) atomicOr(P.status, 4);
+      }
     }
-    if (P.out_ids) P.out_ids[b] = id;
-    if (P.out_cut) P.out_cut[b] = cut;
-    if (P.out_kept) P.out_kept[b] = S.ns;
-    if (P.status && P.out_probs && S.ns > P.out_width) atomicOr(P.status, 2);
+    if (out.id) *out.id = id;
+    if (out.cut) *out.cut = cut;
+    if (out.kept) *out.kept = S.ns;
+    if (P.status && out.probs && S.ns > out.width) atomicOr(P.status, 2);
   }
-  if (P.out_probs || P.out_prob_ids) {
+  if (out.probs || out.prob_ids) {
 #pragma unroll 1
-    for (int j = tid; j < P.out_width; j += NT) {
-      if (P.out_probs) P.out_probs[(size_t)b * P.out_width + j] = (j < ns) ? fw[j] / total : 0.0f;
-      if (P.out_prob_ids) P.out_prob_ids[(size_t)b * P.out_width + j] = (j < ns) ? key_id(sorted[j]) : -1;
+    for (int j = tid; j < out.width; j += NT) {
+      if (out.probs) out.probs[j] = (j < ns) ? fw[j] / total : 0.0f;
+      if (out.prob_ids) out.prob_ids[j] = (j < ns) ? key_id(sorted[j]) : -1;
     }
   }
   __syncthreads();
 }
 
-template <int NT>
+// SHARD: the row is one slice of a vocabulary shared out over ranks: instead of being finished, its
+// candidates (everything at or above the slice's top_k-th score) are handed to the rank that owns
+// the row (shard_exchange.cuh); a row the list cannot vouch for is marked for the streaming kernel.
+template <int NT, bool SHARD>
 __device__ __forceinline__ void finish_list_block(const KParams& P, unsigned char* smem_raw) {
   FLShared& S = *reinterpret_cast<FLShared*>(smem_raw);
   unsigned* hist = reinterpret_cast<unsigned*>(smem_raw + FL_FIXED);
@@ -390,7 +410,7 @@ __device__ __forceinline__ void finish_list_block(const KParams& P, unsigned cha
     if (lane == 0) {
       rc = row_config_from(P, in);
       S.gbest = 0ull; S.vmin = 0xFFFFFFFFu; S.vmax = 0u; S.rmin = 0xFFFFFFFFu; S.rmax = 0u;
-      S.live = 0; S.m = 0; S.redo = 0;
+      S.live = 0; S.m = 0; S.redo = 0; S.nstrict = 0;
     }
   }
   const int bm_words = (V + 31) >> 5;
@@ -449,7 +469,11 @@ __device__ __forceinline__ void finish_list_block(const KParams& P, unsigned cha
   const bool lean = (info & INFO_LEAN) != 0ull;
   const float floor_l = info_floor(info);
   // the next call's filter must find the row's list empty and its word unmarked
-  if (tid == 0) { P.list_info[b] = info & ~INFO_READY; if (lean) P.list_count[b] = 0; }
+  if (tid == 0) {
+    P.list_info[b] = info & ~INFO_READY;
+    if (lean) P.list_count[b] = 0;
+    if (SHARD) P.shard.marks[b] = lean ? 0 : -2;
+  }
   if (!lean) return;  // sample_kernel's row
   const int mode = rc.mode;
   const float s_floor = scaled(floor_l, rc) + 0.0f;
@@ -505,6 +529,43 @@ __device__ __forceinline__ void finish_list_block(const KParams& P, unsigned cha
   float* fx = fw + FL_SORT;
   float* fseg = fx + FL_SORT;
   int c = 0;
+  if (SHARD) {
+    const unsigned epoch = __ldcg(P.shard.epoch);
+    const int owner = b / P.shard.owned;
+    ShardSlot* slot = shard_slot(P.shard, owner, (int)(epoch & 1u), P.shard.rank, b - owner * P.shard.owned);
+    if (!failed && mode != M_ARGMAX_L) {
+      if (S.live == 0) {
+        failed = true;
+      } else {
+        fl_select<NT>(keys, n, rc.k_eff, mode == M_SELECT_MINP, rc.logm, hist, cbuf, S);
+        c = S.m;
+        // the list stands for the slice only if nothing the filter dropped could be a candidate:
+        // top_k candidates strictly above the floor's score (min-p: the threshold itself above it)
+        if (c > P.shard.cap) {
+          failed = true;
+        } else if (mode == M_SELECT_K) {
+          int above = 0;
+#pragma unroll 1
+          for (int i = tid; i < c; i += NT) above += key_value(cbuf[i]) > s_floor ? 1 : 0;
+          above = __reduce_add_sync(FULL, above);
+          if (lane == 0 && above) atomicAdd(&S.nstrict, above);
+          __syncthreads();
+          if (S.nstrict < rc.k_eff) failed = true;
+        } else if (!(unord32(S.vmax) + rc.logm + 0.0f > s_floor)) {
+          failed = true;
+        }
+      }
+    }
+    if (failed) {
+      if (tid == 0) P.shard.marks[b] = -2;  // the streaming kernel takes the row
+      return;
+    }
+#pragma unroll 1
+    for (int i = tid; i < c; i += NT) slot->keys[i] = cbuf[i];
+    if (tid == 0) { slot->best = S.gbest; slot->count = c; }
+    shard_hand_over(P.shard, b, epoch);
+    return;
+  }
   if (!failed && mode != M_ARGMAX_L) {
     c = S.live;
     if (c == 0) {
@@ -532,7 +593,7 @@ __device__ __forceinline__ void finish_list_block(const KParams& P, unsigned cha
     finish_simple(P, b, mode, 0ull, S.gbest, false);
     return;
   }
-  fl_finish<NT>(P, rc, b, cbuf, c, S, fw, fx, fseg, s_floor);
+  fl_finish<NT, true>(P, rc, row_out(P, b), cbuf, c, S, fw, fx, fseg, s_floor);
   if (S.redo) general_row<true>(P, b, smem_raw);
 }
 
@@ -540,6 +601,15 @@ template <int NT>
 __global__ void __launch_bounds__(NT, 1024 / NT) finish_list_kernel(const __grid_constant__ KParams P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   stamp_begin(P.stamps, 1);
-  finish_list_block<NT>(P, smem_raw);
+  finish_list_block<NT, false>(P, smem_raw);
+  stamp_end(P.stamps, 1);
+}
+
+// The same block per row for a vocabulary shard: the slice's candidates go to the row's owner.
+template <int NT>
+__global__ void __launch_bounds__(NT, 1024 / NT) shard_select_kernel(const __grid_constant__ KParams P) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  stamp_begin(P.stamps, 1);
+  finish_list_block<NT, true>(P, smem_raw);
   stamp_end(P.stamps, 1);
 }

@@ -267,7 +267,14 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
   const int vec = pick_vec(P);
   // large aligned rows take the filter path: a floor per row, one streaming filter, then one block
   // per row finishes from the row's list
-  const bool filtered = h->has_list && !h->tune_no_filter && vec == 4 && !P.seen && P.vocab >= kFilterMinVocab;
+  bool filtered = h->has_list && !h->tune_no_filter && vec == 4 && !P.seen && P.vocab >= kFilterMinVocab;
+  if (filtered && P.shard.world > 0) {
+    // a shard with a peer exchange hands listed rows over from the list finish's block only
+    int ht = 0, words = 0;
+    const size_t bytes = lean_shared(P.vocab, P.history_cap, P.history != nullptr,
+                                     P.history ? next_pow2(P.history_cap * 2 < 64 ? 64 : P.history_cap * 2) : 0, &ht, &words);
+    if (bytes == 0 || bytes > (size_t)kMostShared) filtered = false;
+  }
   // 16-bit logits are read by the filter path only (and, row by row, by the multi-pass routine)
   if (P.dtype != 0 && (!filtered || P.cand_count)) return LEAT_E_ARGUMENT;
   // LEAT_FLAG_CLEAR_STATUS: filter_kernel clears the word on the filter path, a memset node otherwise
@@ -291,10 +298,10 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
                      cuda_failed(cudaMemsetAsync(P.list_info, 0, (size_t)h->max_rows * 8, stream), "cudaMemsetAsync")))
       return LEAT_E_CUDA;
     h->dirty = 1;
-    // one small block per row finishes the rows that have lists (not a shard's, which hands its
-    // candidates on); sample_kernel, after it, takes the rest
+    // one small block per row finishes the rows that have lists (or, for a shard with a peer
+    // exchange, hands their candidates to the rows' owners); sample_kernel, after it, takes the rest
     size_t lean_bytes = 0;
-    if (!P.cand_count) {
+    if (!P.cand_count || P.shard.world > 0) {
       lean_bytes = lean_shared(P.vocab, P.history_cap, P.history != nullptr, plan.ht_size, &P.fl_ht, &P.fl_area_words);
       if (lean_bytes > (size_t)kMostShared) lean_bytes = 0;
     }
@@ -332,9 +339,13 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
     if (P.lean) {
       // twice the threads per row while every row's block still finds a place at once
       const bool wide = P.rows <= h->sm_count * 2;
-      const cudaError_t e2 =
-          wide ? launch_dependent(finish_list_kernel<FL_THREADS_WIDE>, dim3(P.rows), dim3(FL_THREADS_WIDE), lean_bytes, stream, P)
-               : launch_dependent(finish_list_kernel<FL_THREADS>, dim3(P.rows), dim3(FL_THREADS), lean_bytes, stream, P);
+      cudaError_t e2;
+      if (P.shard.world > 0)
+        e2 = wide ? launch_dependent(shard_select_kernel<FL_THREADS_WIDE>, dim3(P.rows), dim3(FL_THREADS_WIDE), lean_bytes, stream, P)
+                  : launch_dependent(shard_select_kernel<FL_THREADS>, dim3(P.rows), dim3(FL_THREADS), lean_bytes, stream, P);
+      else
+        e2 = wide ? launch_dependent(finish_list_kernel<FL_THREADS_WIDE>, dim3(P.rows), dim3(FL_THREADS_WIDE), lean_bytes, stream, P)
+                  : launch_dependent(finish_list_kernel<FL_THREADS>, dim3(P.rows), dim3(FL_THREADS), lean_bytes, stream, P);
       if (cuda_failed(e2, "finish_list_kernel launch")) return LEAT_E_CUDA;
       h->launches += 1;
       // ... with a short grid of blocks that look at the rows' flags and mostly leave
@@ -342,10 +353,17 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
       plan.grid_rows = (resident + plan.slices - 1) / plan.slices;
     }
   }
+  if (P.shard.world > 0 && P.lean) {
+    // the rows the select marked (no list, or a list that did not hold up) are streamed; the
+    // blocks of every other row look at the marks and leave
+    P.list = nullptr;
+    P.lean = 0;
+    P.only_rows = P.shard.marks;
+  }
   int rc = pen ? launch_one<true>(P, plan, stream) : launch_one<false>(P, plan, stream);
   if (rc != LEAT_OK) return rc;
   h->launches += 1;
-  if (filtered && P.cand_count) {
+  if (filtered && P.cand_count && P.shard.world == 0) {
     // a shard's rows whose list did not hold up are streamed by a second launch; its blocks leave
     // at once for every other row
     P.list = nullptr;
@@ -699,6 +717,154 @@ int leat_sample_static(const leat_sample_args* a, leat_stream_t stream) {
   if (cuda_failed(cudaMemsetAsync(h->ws + h->L.ticket, 0, h->L.total - h->L.ticket, s), "cudaMemsetAsync"))
     return LEAT_E_CUDA;
   return launch_sample(h, P, s);
+}
+
+// ---- vocabulary shards with a peer exchange ------------------------------------------------------
+
+struct leat_shard {
+  leat_sampler* h;
+  ShardView view;
+  int finish_shared;
+};
+
+namespace {
+// the rank's own words behind the exchange part of its region: step number, tickets, marks
+size_t shard_private_at(int world, int owned, int cap) { return shard_region_bytes(world, owned, cap); }
+size_t shard_private_bytes(int rows) { return 256 + ((size_t)rows * 4 + 255) / 256 * 256; }
+}  // namespace
+
+size_t leat_shard_region_bytes(int32_t rows, int32_t cap, int32_t world) {
+  if (rows <= 0 || cap <= 0 || world <= 0 || world > SHARD_MAX_WORLD) return 0;
+  const int owned = (rows + world - 1) / world;
+  return shard_private_at(world, owned, cap) + shard_private_bytes(rows);
+}
+
+int leat_peer_alloc(size_t bytes, void** ptr, unsigned char* handle) {
+  if (!ptr || !handle || bytes == 0) return LEAT_E_ARGUMENT;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is exchanged as 64 bytes");
+  void* p = nullptr;
+  if (cuda_failed(cudaMalloc(&p, bytes), "cudaMalloc")) return LEAT_E_CUDA;
+  cudaIpcMemHandle_t ipc;
+  if (cuda_failed(cudaMemset(p, 0, bytes), "cudaMemset") || cuda_failed(cudaDeviceSynchronize(), "cudaDeviceSynchronize") ||
+      cuda_failed(cudaIpcGetMemHandle(&ipc, p), "cudaIpcGetMemHandle")) {
+    cudaFree(p);
+    return LEAT_E_CUDA;
+  }
+  memcpy(handle, &ipc, 64);
+  *ptr = p;
+  return LEAT_OK;
+}
+
+int leat_peer_open(const unsigned char* handle, void** ptr) {
+  if (!ptr || !handle) return LEAT_E_ARGUMENT;
+  cudaIpcMemHandle_t ipc;
+  memcpy(&ipc, handle, 64);
+  return cuda_failed(cudaIpcOpenMemHandle(ptr, ipc, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle") ? LEAT_E_CUDA : LEAT_OK;
+}
+
+int leat_peer_close(void* ptr) {
+  return cuda_failed(cudaIpcCloseMemHandle(ptr), "cudaIpcCloseMemHandle") ? LEAT_E_CUDA : LEAT_OK;
+}
+
+int leat_peer_free(void* ptr) { return cuda_failed(cudaFree(ptr), "cudaFree") ? LEAT_E_CUDA : LEAT_OK; }
+
+int leat_shard_create(leat_sampler_t* h, int32_t rank, int32_t world, int32_t rows, int32_t cap, void* const* regions,
+                      leat_shard_t** out) {
+  if (!h || !regions || !out || world <= 0 || world > SHARD_MAX_WORLD || rank < 0 || rank >= world || rows <= 0 || cap <= 0)
+    return LEAT_E_ARGUMENT;
+  if (rows > h->max_rows || cap > FL_SORT) return LEAT_E_CAPACITY;
+  leat_shard* s = new (std::nothrow) leat_shard();
+  if (!s) return LEAT_E_ARGUMENT;
+  s->h = h;
+  ShardView& v = s->view;
+  memset(&v, 0, sizeof(v));
+  for (int r = 0; r < world; ++r) {
+    if (!regions[r]) { delete s; return LEAT_E_ARGUMENT; }
+    v.region[r] = static_cast<unsigned char*>(regions[r]);
+  }
+  v.rank = rank; v.world = world; v.rows = rows; v.owned = (rows + world - 1) / world; v.cap = cap;
+  unsigned char* mine = v.region[rank] + shard_private_at(world, v.owned, cap);
+  v.epoch = reinterpret_cast<unsigned*>(mine);
+  v.tickets = v.epoch + 8;
+  v.done_ticket = v.epoch + 24;
+  v.marks = reinterpret_cast<int*>(mine + 256);
+  const unsigned one = 1u;  // steps count from 1: a region is all zeros before its first step
+  if (cuda_failed(cudaMemcpy(v.epoch, &one, sizeof(one), cudaMemcpyHostToDevice), "cudaMemcpy")) { delete s; return LEAT_E_CUDA; }
+  s->finish_shared = FL_FIXED + FL_HIST_WORDS * 4 + FL_KEYS * 8 + FL_AREA_MIN_WORDS * 4;
+  const int most = kMostShared;
+  if (allow_shared(shard_select_kernel<FL_THREADS>, most) || allow_shared(shard_select_kernel<FL_THREADS_WIDE>, most) ||
+      allow_shared(shard_finish_kernel<FL_THREADS>, most) || allow_shared(shard_finish_kernel<FL_THREADS_WIDE>, most)) {
+    delete s;
+    return LEAT_E_CUDA;
+  }
+  *out = s;
+  return LEAT_OK;
+}
+
+int leat_shard_destroy(leat_shard_t* shard) {
+  delete shard;
+  return LEAT_OK;
+}
+
+int leat_shard_select(leat_shard_t* s, const leat_sample_args* a, leat_stream_t stream) {
+  if (!s || !a) return LEAT_E_ARGUMENT;
+  if (a->rows != s->view.rows) return LEAT_E_ARGUMENT;
+  KParams P;
+  int rc = fill_params(s->h, a, P);
+  if (rc != LEAT_OK) return rc;
+  P.shard = s->view;
+  P.cand_count = s->view.marks;  // (what marks the call as a shard's for the streaming kernel)
+  P.cand_cap = s->view.cap;
+  return launch_sample(s->h, P, static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+int shard_tail(leat_shard* s, const leat_sample_args* a, KParams& P) {
+  if (!s || !a) return LEAT_E_ARGUMENT;
+  if (a->rows != s->view.rows) return LEAT_E_ARGUMENT;
+  // the handle is sized for this rank's slice; here `vocab` is the whole vocabulary's size
+  leat_sample_args whole = *a;
+  const int vocab = a->vocab_total > 0 ? a->vocab_total : a->vocab;
+  whole.vocab = 1;
+  whole.vocab_total = 0;
+  int rc = fill_params(s->h, &whole, P);
+  if (rc != LEAT_OK) return rc;
+  if (!a->out_ids || vocab <= 0) return LEAT_E_ARGUMENT;
+  P.vocab = vocab; P.vocab_total = vocab;
+  P.shard = s->view;
+  int dev = -1;
+  if (cuda_failed(cudaGetDevice(&dev), "cudaGetDevice")) return LEAT_E_CUDA;
+  if (dev != s->h->device) return LEAT_E_DEVICE;
+  return LEAT_OK;
+}
+}  // namespace
+
+int leat_shard_finish(leat_shard_t* s, const leat_sample_args* a, leat_stream_t stream) {
+  KParams P;
+  int rc = shard_tail(s, a, P);
+  if (rc != LEAT_OK) return rc;
+  const ShardView& v = s->view;
+  const int mine = v.rows - v.rank * v.owned < v.owned ? v.rows - v.rank * v.owned : v.owned;
+  s->h->launches = 0;
+  if (mine <= 0) return LEAT_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool wide = mine <= s->h->sm_count * 2;
+  const cudaError_t e =
+      wide ? launch_dependent(shard_finish_kernel<FL_THREADS_WIDE>, dim3(mine), dim3(FL_THREADS_WIDE), (size_t)s->finish_shared, st, P)
+           : launch_dependent(shard_finish_kernel<FL_THREADS>, dim3(mine), dim3(FL_THREADS), (size_t)s->finish_shared, st, P);
+  if (cuda_failed(e, "shard_finish_kernel launch")) return LEAT_E_CUDA;
+  s->h->launches = 1;
+  return LEAT_OK;
+}
+
+int leat_shard_result(leat_shard_t* s, const leat_sample_args* a, leat_stream_t stream) {
+  KParams P;
+  int rc = shard_tail(s, a, P);
+  if (rc != LEAT_OK) return rc;
+  if (cuda_failed(launch_dependent(shard_result_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), P),
+                  "shard_result_kernel launch")) return LEAT_E_CUDA;
+  s->h->launches = 1;
+  return LEAT_OK;
 }
 
 }  // extern "C"

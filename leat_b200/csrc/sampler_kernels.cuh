@@ -41,6 +41,8 @@ constexpr int HASH_EMPTY = -1;
 constexpr int NO_ID = 0x7FFFFFFF;
 constexpr float GUMBEL_MAX = 17.0f;  // above -log(-log(1 - 2^-24)) = 16.64
 
+#include "shard_exchange.cuh"
+
 struct KParams {
   const float* logits; int rows; int vocab; long long row_stride; int vocab_total;
   int dtype;  // what `logits` really points at: 0 float32, 1 bfloat16, 2 float16 (row_stride in logits)
@@ -79,6 +81,8 @@ struct KParams {
   int lean; int fl_area_words; int fl_ht;
   // measurement aid (device_util.cuh: stamp_begin / stamp_end), or null
   unsigned long long* stamps;
+  // vocabulary shards with a peer exchange (shard_exchange.cuh); world = 0: not in use
+  ShardView shard;
 };
 
 struct RowCfg {
@@ -248,7 +252,7 @@ __device__ inline RowCfg row_config_from(const KParams& P, const RowIn& in) {
   else if (rc.k_eff <= P.k_max) rc.mode = M_SELECT_K;
   else if (!(rc.k > 0.0f) && !(rc.p < 1.0f) && rc.m > 0.0f) rc.mode = M_SELECT_MINP;
   else rc.mode = M_GENERAL;
-  rc.track = (P.out_greedy != nullptr || P.cand_best != nullptr || rc.mode == M_ARGMAX_L) ? 1 : 0;
+  rc.track = (P.out_greedy != nullptr || P.cand_best != nullptr || P.shard.world > 0 || rc.mode == M_ARGMAX_L) ? 1 : 0;
   return rc;
 }
 
@@ -988,6 +992,9 @@ static_assert(sizeof(Shared) <= 256 && sizeof(Ctx) <= 128 && sizeof(RowCfg) <= 1
 
 #include "finish_list.cuh"
 
+#define LEAT_SHARD_KERNELS
+#include "shard_exchange.cuh"
+
 // One (row, slice) of sample_kernel's work, by the whole block.
 template <bool PEN>
 __device__ __forceinline__ void sample_block(const KParams& P, const int b, const int slice, unsigned char* smem_raw) {
@@ -1330,6 +1337,26 @@ __device__ __forceinline__ void sample_block(const KParams& P, const int b, cons
   __syncthreads();
 
   // ---- the row is whole in this block ----
+  if (P.shard.world > 0) {  // shards with a peer exchange: the row's candidates go to its owner
+    const unsigned epoch = __ldcg(P.shard.epoch);
+    ShardSlot* slot = shard_slot(P.shard, b / P.shard.owned, (int)(epoch & 1u), P.shard.rank, b - (b / P.shard.owned) * P.shard.owned);
+    int n = 0;
+    if (!failed && (mode == M_SELECT_K || mode == M_SELECT_MINP)) {
+      n = sm.n;
+      if (n > P.shard.cap) { n = 0; failed = true; }
+#pragma unroll 1
+      for (int i = tid; i < n; i += nt) slot->keys[i] = buf[i];
+    } else if (!failed && mode == M_ARGMAX_G) {
+      n = 1;
+      if (tid == 0) slot->keys[0] = sm.best;
+    }
+    if (tid == 0) {
+      slot->best = sm.gbest;
+      slot->count = (failed || mode == M_GENERAL) ? -1 : n;
+    }
+    shard_hand_over(P.shard, b, epoch);
+    return;
+  }
   if (P.cand_count) {  // shard mode: hand the row's candidates to the gather
     const int cap = P.cand_cap;
     int n = 0;
@@ -1381,11 +1408,13 @@ template <bool PEN>
 __global__ void __launch_bounds__(512, 2) sample_kernel(const __grid_constant__ KParams P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   stamp_begin(P.stamps, 2);
-  if (P.lean) {
-    // after the list finish most calls leave nothing to do here: the filter's flags say so
+  if (P.lean || P.only_rows) {
+    // after the list finish most calls leave nothing to do here: the filter's flags (or the marks
+    // of the rows a shard's lists could not settle) say so
     int any = 0;
 #pragma unroll 1
-    for (int i = threadIdx.x; i < P.rows; i += blockDim.x) any |= (__ldcg(&P.list_info[i]) & INFO_LEAN) == 0ull;
+    for (int i = threadIdx.x; i < P.rows; i += blockDim.x)
+      any |= P.only_rows ? (__ldcg(&P.only_rows[i]) == -2) : ((__ldcg(&P.list_info[i]) & INFO_LEAN) == 0ull);
     if (!__syncthreads_or(any)) {
       // this grid must not be over before the list finish is: what follows it in the stream may
       // depend on this grid alone

@@ -127,8 +127,9 @@ def test_verify_draft_accepts_and_rejects(device):
 
 
 def test_sharded_sampler_over_nccl_with_one_rank(device):
-    """The host class end to end on a real process group (one rank: the all-gather of the packed
-    records is then a copy), against the oracle."""
+    """The host class end to end on a real process group with both exchanges (one rank: the
+    all-gather of the packed records is then a copy, and the peer exchange stores into the rank's
+    own region), against the oracle."""
     import os
     import socket
 
@@ -146,13 +147,24 @@ def test_sharded_sampler_over_nccl_with_one_rank(device):
     dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
     try:
         w = workloads.config5(rows=16, vocab=201088)
-        sharded = ShardedSampler(w.rows, w.vocab, k_max=64, cap=128, device=device)
         t = lambda x: torch.as_tensor(x).to(device)  # noqa: E731
         seed = torch.as_tensor(w.seed.astype(np.int64)).to(device).to(torch.uint32)
+        want = helpers.oracle_run(w, "U")
+        sharded = ShardedSampler(w.rows, w.vocab, k_max=64, cap=128, device=device, exchange="collective")
         got = sharded.sample(t(w.logits), t(w.options), seed, t(w.position), history=t(w.history),
                              penalties=t(w.penalties), uniform=t(w.uniform), width=64)  # fmt: skip
         torch.cuda.synchronize()
-        helpers.compare(helpers.oracle_run(w, "U"), got, 64, max_fragile=0)
+        helpers.compare(want, got, 64, max_fragile=0)
+        peer = ShardedSampler(w.rows, w.vocab, k_max=64, cap=128, device=device, exchange="peer")
+        assert peer.exchange_kind == "peer"
+        for _ in range(3):
+            got = peer.sample(t(w.logits), t(w.options), seed, t(w.position), history=t(w.history),
+                              penalties=t(w.penalties), uniform=t(w.uniform))  # fmt: skip
+            torch.cuda.synchronize()
+            helpers.compare(want, got, 0, max_fragile=0)
+            np.testing.assert_array_equal(got.kept.cpu().numpy(), want.kept)
+            np.testing.assert_array_equal(got.cut.cpu().numpy(), want.cut)
+        peer.close()
     finally:
         dist.destroy_process_group()
 
