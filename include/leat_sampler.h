@@ -138,9 +138,10 @@ int leat_sampler_plan(const leat_sampler_t* handle, int32_t rows, int32_t vocab,
 int leat_sampler_last_launches(const leat_sampler_t* handle);
 /* Measurement aid.  While enabled, the kernels of a call on this handle record, in the workspace,
    when their first block began and their last block ended (the GPU's nanosecond timer), also inside
-   a captured CUDA graph.  leat_sampler_kernel_times waits for the device and writes eight offsets in
+   a captured CUDA graph.  leat_sampler_kernel_times waits for the device and writes twelve offsets in
    milliseconds from the first begin of the last call: begin and end of filter_kernel,
-   finish_list_kernel, sample_kernel and floor_kernel (-1, -1 for a kernel the call did not launch).  Kernels of
+   finish_list_kernel (a shard's: shard_select_kernel), sample_kernel, floor_kernel,
+   shard_finish_kernel and shard_result_kernel (-1, -1 for a kernel the call did not launch).  Kernels of
    one call overlap (each is a programmatic dependent of the one before), which the offsets show. */
 int leat_sampler_time_kernels(leat_sampler_t* handle, int32_t enabled);
 int leat_sampler_kernel_times(leat_sampler_t* handle, float* milliseconds);

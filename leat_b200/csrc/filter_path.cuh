@@ -25,7 +25,6 @@
 
 constexpr int SAMPLE_CHUNKS = 256;   // chunks of the sample, one per thread of floor_kernel
 constexpr int SAMPLE_CHUNK_BYTES = 128;  // a chunk is one 128-byte line: 32 float32 logits, 64 16-bit ones
-constexpr int SAMPLE_SIZE = SAMPLE_CHUNKS * 32;  // logits of a float32 row's sample (16-bit rows: twice that)
 constexpr int SAMPLE_MAX_ORDER = 96; // deepest order statistic of the chunk maxima that is trusted
 constexpr int FILTER_THREADS = 256;
 constexpr int FILTER_VECS = 8;       // 128-bit loads in flight per thread
@@ -166,28 +165,43 @@ __device__ __forceinline__ float logit_at(const KParams& P, int b, int i) {
   return __half2float(__ushort_as_half(h));
 }
 
+// Vectors of 16 bytes per chunk of the sample: eight (a 128-byte line) unless the row is short;
+// the sample stays under an eighth of the row (a vocabulary slice of 25 000 tokens gives 2048 of
+// them, not 8192).
+__device__ __forceinline__ int sample_vecs(int V, int per_vec) {
+  int vecs = SAMPLE_CHUNK_BYTES / 16;
+  while (vecs > 1 && (long long)SAMPLE_CHUNKS * vecs * per_vec * 8 > V) vecs >>= 1;
+  return vecs;
+}
+
 // The descending chunk maxima of a row's sample, by the first SAMPLE_CHUNKS threads of the calling
 // block (whole warps; every thread of the block must call); `runs` is SAMPLE_CHUNKS 8-byte words of
-// shared memory, `sorted` as many floats.  Rows are 16-byte aligned whole vectors, at least
-// 2 * SAMPLE_SIZE logits long (so that the chunks do not overlap).
+// shared memory, `sorted` as many floats.  Rows are 16-byte aligned whole vectors, at least twice
+// the sample long (so that the chunks do not overlap).
+template <typename T, int VECS>
+__device__ __forceinline__ float chunk_maximum(const void* row, int V) {
+  // four chunks in a row make a piece; piece p starts at a multiple of its own length near p * V / 64
+  const int tid = threadIdx.x;
+  constexpr long long CHUNK = VECS * T::PER_VEC;  // logits
+  constexpr int PIECES = SAMPLE_CHUNKS / 4;
+  const long long at = (((long long)(tid >> 2) * V / PIECES) & ~(4 * CHUNK - 1)) + (tid & 3) * CHUNK;
+  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(row) + at * (16 / T::PER_VEC));
+  uint4 x[VECS];
+#pragma unroll
+  for (int u = 0; u < VECS; ++u) x[u] = __ldg(src + u);
+  float m = neg_inf();  // fmaxf drops NaNs
+#pragma unroll
+  for (int u = 0; u < VECS; ++u) m = fmaxf(m, vec_max<T>(x[u]));
+  return m;
+}
+
 template <typename T>
-__device__ __forceinline__ void sample_maxima(const void* row, int V, unsigned long long* runs, float* sorted) {
+__device__ __forceinline__ void sample_maxima(const void* row, int V, int vecs, unsigned long long* runs, float* sorted) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   unsigned long long key = 0ull;
   if (tid < SAMPLE_CHUNKS) {
-    // four chunks in a row make a piece of 512 bytes; piece p starts at a multiple of its own
-    // length near p * V / 64
-    constexpr int VECS = SAMPLE_CHUNK_BYTES / 16;
-    constexpr long long CHUNK = VECS * T::PER_VEC;  // logits
-    constexpr int PIECES = SAMPLE_CHUNKS / 4;
-    const long long at = (((long long)(tid >> 2) * V / PIECES) & ~(4 * CHUNK - 1)) + (tid & 3) * CHUNK;
-    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(row) + at * (16 / T::PER_VEC));
-    uint4 x[VECS];
-#pragma unroll
-    for (int u = 0; u < VECS; ++u) x[u] = __ldg(src + u);
-    float m = neg_inf();  // fmaxf drops NaNs
-#pragma unroll
-    for (int u = 0; u < VECS; ++u) m = fmaxf(m, vec_max<T>(x[u]));
+    const float m = vecs == 8 ? chunk_maximum<T, 8>(row, V) : vecs == 4 ? chunk_maximum<T, 4>(row, V)
+                  : vecs == 2 ? chunk_maximum<T, 2>(row, V) : chunk_maximum<T, 1>(row, V);
     // ordered like the candidates' keys: value first, the chunk's number breaking ties
     key = make_key(m, (uint32_t)tid);
     // every warp sorts its 32 maxima in registers (a bitonic network over shuffles) ...
@@ -270,8 +284,9 @@ __device__ __forceinline__ float block_floor(const KParams& P, int b, unsigned l
     if (tid == 0) *rc = row_config_from(P, in);
   }
   const unsigned char* row = reinterpret_cast<const unsigned char*>(P.logits) + (size_t)b * P.row_stride * (16 / T::PER_VEC);
-  sample_maxima<T>(row, P.vocab, runs, sorted);
-  const float floor_l = floor_from_sample(*rc, P.vocab, SAMPLE_CHUNKS * (SAMPLE_CHUNK_BYTES / 16) * T::PER_VEC, P.list_cap, sorted);
+  const int vecs = sample_vecs(P.vocab, T::PER_VEC);
+  sample_maxima<T>(row, P.vocab, vecs, runs, sorted);
+  const float floor_l = floor_from_sample(*rc, P.vocab, SAMPLE_CHUNKS * vecs * T::PER_VEC, P.list_cap, sorted);
   if (tid == 0)
     P.list_info[b] = INFO_READY | (lean_takes(P, *rc, floor_l) ? INFO_LEAN : 0ull) | (unsigned long long)__float_as_uint(floor_l);
   return floor_l;

@@ -251,7 +251,7 @@ int launch_one(const KParams& P, const Plan& plan, cudaStream_t stream) {
   dim3 grid(plan.slices, plan.grid_rows > 0 && plan.grid_rows < P.rows ? plan.grid_rows : P.rows);
   // after the list finish the blocks may move in early (the filter's floors and flags are final by
   // then); straight after a filter launch they must not
-  const cudaError_t e = (P.list && P.lean) ? launch_dependent(sample_kernel<PEN>, grid, dim3(plan.threads), (size_t)plan.shared, stream, P)
+  const cudaError_t e = ((P.list && P.lean) || (P.shard.world > 0 && P.only_rows)) ? launch_dependent(sample_kernel<PEN>, grid, dim3(plan.threads), (size_t)plan.shared, stream, P)
                                : (sample_kernel<PEN><<<grid, plan.threads, plan.shared, stream>>>(P), cudaGetLastError());
   return cuda_failed(e, "sample_kernel launch") ? LEAT_E_CUDA : LEAT_OK;
 }
@@ -476,9 +476,9 @@ int leat_sampler_kernel_times(leat_sampler_t* h, float* milliseconds) {
       cuda_failed(cudaMemcpy(stamps, h->ws + h->L.stamps, sizeof(stamps), cudaMemcpyDeviceToHost), "cudaMemcpy"))
     return LEAT_E_CUDA;
   unsigned long long first = ~0ull;
-  for (int k = 0; k < 4; ++k)
+  for (int k = 0; k < 6; ++k)
     if (stamps[2 * k] && ~stamps[2 * k] < first) first = ~stamps[2 * k];
-  for (int k = 0; k < 4; ++k) {
+  for (int k = 0; k < 6; ++k) {
     const bool ran = stamps[2 * k] != 0ull;
     milliseconds[2 * k] = ran ? (float)((double)(~stamps[2 * k] - first) * 1e-6) : -1.0f;
     milliseconds[2 * k + 1] = ran ? (float)((double)(stamps[2 * k + 1] - first) * 1e-6) : -1.0f;
@@ -832,6 +832,7 @@ int shard_tail(leat_shard* s, const leat_sample_args* a, KParams& P) {
   if (!a->out_ids || vocab <= 0) return LEAT_E_ARGUMENT;
   P.vocab = vocab; P.vocab_total = vocab;
   P.shard = s->view;
+  if (s->h->timing) P.stamps = reinterpret_cast<unsigned long long*>(s->h->ws + s->h->L.stamps);
   int dev = -1;
   if (cuda_failed(cudaGetDevice(&dev), "cudaGetDevice")) return LEAT_E_CUDA;
   if (dev != s->h->device) return LEAT_E_DEVICE;

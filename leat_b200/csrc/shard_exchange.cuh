@@ -99,9 +99,9 @@ __device__ __forceinline__ ShardSlot* shard_slot(const ShardView& v, int owner, 
 // the row is counted, and the block that counts the owner's last row raises the owner's flag.  The
 // whole block calls it.
 __device__ __forceinline__ void shard_hand_over(const ShardView& v, int row, unsigned epoch) {
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();  // the block's stores are ordered before thread 0's fence
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const int owner = row / v.owned;
     const int theirs = min(v.owned, v.rows - owner * v.owned);
     const unsigned ticket = atomicAdd(&v.tickets[owner], 1u);
@@ -148,6 +148,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) shard_finish_kernel(const __gri
     for (int i = tid; i < BINS / 4; i += NT) h4[i] = make_uint4(0u, 0u, 0u, 0u);
   }
   grid_dependency_wait();  // this rank's own hand-overs (and its step number) are settled
+  stamp_begin(P.stamps, 4);
   const unsigned epoch = __ldcg(v.epoch);
   const int parity = (int)(epoch & 1u);
   // ---- every rank's flag, each polled by a thread of its own ----
@@ -232,9 +233,9 @@ __global__ void __launch_bounds__(NT, 1024 / NT) shard_finish_kernel(const __gri
                        (size_t)parity * v.world * v.owned + b;
     *reinterpret_cast<int4*>(dst) = *reinterpret_cast<const int4*>(&result);
   }
-  __threadfence_system();
   __syncthreads();
   if (tid == 0) {
+    __threadfence_system();
     const int mine = min(v.owned, v.rows - v.rank * v.owned);
     const unsigned ticket = atomicAdd(v.done_ticket, 1u);
     S.sel_bin = ticket == (unsigned)(mine - 1) ? 1 : 0;
@@ -246,6 +247,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) shard_finish_kernel(const __gri
     unsigned* done = reinterpret_cast<unsigned*>(v.region[tid] + shard_at_done(v.world, v.owned, v.cap));
     store_release_system(&done[parity * v.world + v.rank], epoch);
   }
+  stamp_end(P.stamps, 4);
 }
 
 // One block: waits for every owner's flag, copies the results out and ends the step.
@@ -253,6 +255,7 @@ __global__ void __launch_bounds__(256) shard_result_kernel(const __grid_constant
   const ShardView& v = P.shard;
   const int tid = threadIdx.x;
   grid_dependency_wait();
+  stamp_begin(P.stamps, 5);
   const unsigned epoch = __ldcg(v.epoch);
   const int parity = (int)(epoch & 1u);
   int arrived = 1;
@@ -278,6 +281,7 @@ __global__ void __launch_bounds__(256) shard_result_kernel(const __grid_constant
     if (!all_here && P.status) atomicOr(P.status, 12);
     *v.epoch = epoch + 1u;  // the step is over on this rank
   }
+  stamp_end(P.stamps, 5);
 }
 
 #endif  // LEAT_SHARD_KERNELS

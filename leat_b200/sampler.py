@@ -102,12 +102,12 @@ class Sampler:
         """Measurement aid: the kernels of each call stamp their begin and end (also under graph capture)."""
         _lib.check(_lib.lib.leat_sampler_time_kernels(self.handle, int(enabled)), "leat_sampler_time_kernels")
 
-    KERNELS = ("filter_kernel", "finish_list_kernel", "sample_kernel", "floor_kernel")
+    KERNELS = ("filter_kernel", "finish_list_kernel", "sample_kernel", "floor_kernel", "shard_finish_kernel", "shard_result_kernel")
 
     def kernel_times(self) -> dict[str, tuple[float, float]]:
         """Begin and end of each kernel of the last call, milliseconds from the first begin (waits for
         the device); kernels the call did not launch are left out."""
-        out = (_lib.C.c_float * 8)()
+        out = (_lib.C.c_float * 12)()
         _lib.check(_lib.lib.leat_sampler_kernel_times(self.handle, out), "leat_sampler_kernel_times")
         return {name: (float(out[2 * k]), float(out[2 * k + 1])) for k, name in enumerate(self.KERNELS) if out[2 * k] >= 0}
 
