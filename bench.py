@@ -475,6 +475,7 @@ def run_sharded(args) -> None:
         keep_busy(replay, ms)
     dist.barrier()
     torch.cuda.synchronize()
+    replayed_ids = out.clone()  # what the last of the replayed steps left (checked below)
     # end to end: this rank's slice comes from pinned host memory every step, the ids go back
     host_slice = torch.as_tensor(np.ascontiguousarray(w.logits[:, start:stop])).pin_memory()
     host_ids = torch.empty((w.rows, 1), dtype=torch.int32).pin_memory()
@@ -501,6 +502,9 @@ def run_sharded(args) -> None:
     torch.cuda.synchronize()
     everyone = [torch.empty_like(result.ids) for _ in range(world)]
     dist.all_gather(everyone, result.ids.contiguous())
+    # (every step had the same inputs: the last replayed step must have given the same ids)
+    stale = (replayed_ids != result.ids).sum().to(torch.int64)
+    dist.all_reduce(stale)
     parity = None
     if rank == 0:
         ids = result.ids.cpu().numpy().ravel()
@@ -514,7 +518,9 @@ def run_sharded(args) -> None:
                                       | (cut != one.cut.cpu().numpy())))  # fmt: skip
         parity = oracle_parity(w, ids, kept, cut, CPU_SAMPLE_ROWS)
         parity.update({"rows": w.rows, "ranks_differing": differing_ranks, "rows_differing_from_one_gpu": vs_one,
-                       "mismatch": parity["oracle_mismatch"] + vs_one + differing_ranks, "fragile": parity["oracle_fragile"],
+                       "ids_differing_after_replays": int(stale.item()),
+                       "mismatch": parity["oracle_mismatch"] + vs_one + differing_ranks + int(stale.item()),
+                       "fragile": parity["oracle_fragile"],
                        "status_word": int(result.status.item())})  # fmt: skip
         del single, one
         achieved = w.logit_bytes / world / (ms * 1e-3) / 1e9  # per GPU: each reads its slice once

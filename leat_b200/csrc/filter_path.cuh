@@ -383,21 +383,20 @@ __device__ __forceinline__ void filter_process(const KParams& P, FilterStage& st
   if (st.held + total > FILTER_STAGE) filter_flush(P, st);
   if (hot) {
     int at = st.held + incl - count;
-    // the few logits that made it are read again (from L2) by their index: no register array is
-    // indexed by a run-time number
-#pragma unroll 1
-    while (hits) {
-      const int bit = __ffsll((long long)hits) - 1;
-      hits &= hits - 1ull;
-      const int i = base + ((bit / T::PER_VEC) * NT + tid) * T::PER_VEC + (bit % T::PER_VEC);
-      float l;
-      if constexpr (T::PER_VEC == 4) {
-        l = reinterpret_cast<const float*>(row)[i];
-      } else {
-        const unsigned short h = reinterpret_cast<const unsigned short*>(row)[i];
-        l = std::is_same<T, BF16>::value ? __uint_as_float((uint32_t)h << 16) : __half2float(__ushort_as_half(h));
+    // the few logits that made it go to the stage straight from the registers: every vector and
+    // element is looked at under a predicate, so no register array is indexed by a run-time number
+    // and nothing is read again
+#pragma unroll
+    for (int u = 0; u < FILTER_VECS; ++u) {
+      const uint32_t bits = (uint32_t)(hits >> (T::PER_VEC * u)) & ((1u << T::PER_VEC) - 1u);
+      if (bits) {
+        float f[T::PER_VEC];
+        vec_to_floats<T>(x[u], f);
+        const int i0 = base + (u * NT + tid) * T::PER_VEC;
+#pragma unroll
+        for (int e = 0; e < T::PER_VEC; ++e)
+          if ((bits >> e) & 1u) st.mine[at++] = ((unsigned long long)__float_as_uint(f[e]) << 32) | (uint32_t)(i0 + e);
       }
-      st.mine[at++] = ((unsigned long long)__float_as_uint(l) << 32) | (uint32_t)i;
     }
   }
   st.held += total;

@@ -99,9 +99,13 @@ __device__ __forceinline__ ShardSlot* shard_slot(const ShardView& v, int owner, 
 // the row is counted, and the block that counts the owner's last row raises the owner's flag.  The
 // whole block calls it.
 __device__ __forceinline__ void shard_hand_over(const ShardView& v, int row, unsigned epoch) {
-  __syncthreads();  // the block's stores are ordered before thread 0's fence
+  // The block's stores are ordered before thread 0's fence by the barrier, and before the ticket by
+  // the fence; device scope is enough here, because the one block that goes on to raise the flag
+  // fences at system scope after it has seen every other block's ticket (fences are cumulative).
+  // A system fence per block was measured at about 10 us per 512 blocks.
+  __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
+    __threadfence();
     const int owner = row / v.owned;
     const int theirs = min(v.owned, v.rows - owner * v.owned);
     const unsigned ticket = atomicAdd(&v.tickets[owner], 1u);
@@ -235,7 +239,7 @@ __global__ void __launch_bounds__(NT, 1024 / NT) shard_finish_kernel(const __gri
   }
   __syncthreads();
   if (tid == 0) {
-    __threadfence_system();
+    __threadfence();  // (device scope: the last block fences at system scope below, as in shard_hand_over)
     const int mine = min(v.owned, v.rows - v.rank * v.owned);
     const unsigned ticket = atomicAdd(v.done_ticket, 1u);
     S.sel_bin = ticket == (unsigned)(mine - 1) ? 1 : 0;
