@@ -107,6 +107,13 @@ typedef struct leat_sample_args {
   int32_t* out_prob_ids; /* (rows, out_width) their ids, -1-padded */
   int32_t out_width;
   int32_t* status;       /* one int32, OR-ed with LEAT_STATUS_*; may be NULL */
+  /* extension: the model's soft cap on its logits, logits = tanh(logits / cap) * cap
+     (leat/model.py:419-423), applied here to the few logits that reach a row's floor instead of by
+     a pass of its own over (rows, vocab); 0: none.  Evaluated in double precision and rounded to
+     float32.  Rows that cannot take the list path are then settled by the multi-pass routine. */
+  float softcap;
+  /* the position of every row when `position` is NULL (leat/sampler.py:41-42 takes an int too) */
+  int32_t position_scalar;
 } leat_sample_args;
 
 /* Bytes of device workspace a handle needs for calls of up to max_rows x max_vocab with
@@ -158,12 +165,15 @@ int leat_sample(leat_sampler_t* handle, const leat_sample_args* args, leat_strea
    device-wide synchronisation.  It has no counterpart in the reference (leat's kernels allocate
    their scratch per call).  The scratch the blocks of a row exchange lives in a fixed array of
    about 1.1 MB inside the library, held by every GPU that loads the library until the process
-   exits.  Limits: rows <= 64, vocab <= 262144, top_k <= 64 on the single-pass path; a larger call
-   returns LEAT_E_CAPACITY.  The caller still passes every input and output buffer.  The first call
-   on a device looks up the array's device address and raises the kernels' shared-memory limit,
-   so make that first call outside any stream capture.  All calls on a device share the one array:
-   calls that overlap on the GPU (different streams) race; issue them on one stream or order them.
-   Calls cudaMalloc, cudaFree or any allocating routine nowhere. */
+   exits.  Limits: rows <= 64 and vocab <= 262144, else LEAT_E_CAPACITY; float32 logits only
+   (LEAT_FLAG_LOGITS_BF16 / _F16: LEAT_E_ARGUMENT); rows with top_k <= 64 take the single pass,
+   rows with a larger top_k (or none, with top_p < 1) are settled by the slower multi-pass routine,
+   as with a handle created for k_max = 64.  The caller still passes every input and output buffer.
+   The first call on a device looks up the array's device address and raises the kernels'
+   shared-memory limit (under a lock: threads may race to it), so make that first call outside any
+   stream capture.  All calls on a device share the one array: calls that overlap on the GPU
+   (different streams) race; issue them on one stream or order them.  Calls cudaMalloc, cudaFree
+   or any allocating routine nowhere. */
 int leat_sample_static(const leat_sample_args* args, leat_stream_t stream);
 
 /* ops.argmax(): leat/ops.py:496-500 and leat/kernels/argmax.py:48-61.  x (rows, vocab) float32 ->
@@ -185,6 +195,19 @@ int leat_cutoff(leat_sampler_t* handle, const float* scores, int32_t rows, int32
    drafted[0..accepted) then sampled[accepted]. */
 int leat_verify_draft(const int32_t* drafted, const int32_t* sampled, const int32_t* greedy,
                       int32_t n, int32_t drafts, int32_t* accepted, int32_t* tokens,
+                      leat_stream_t stream);
+
+/* What follows a speculative step's verification on the device, so that the next step needs no
+   host round trip (leat/engine.py:609-631, :677-686): sequence i ran its last token and `drafts`
+   drafts, of which `accepted[i]` are kept.  Its slot's history (leat_b200's sparse form of leat's
+   `_seen` mask: ids (slots, capacity) int32 used as a ring, count (slots,) int32) takes the tokens
+   that were run up to the kept row, last[i] then drafted[i, 0..accepted[i]), markup left out (text
+   (vocab,) bytes, non-zero = a penalty may lower the token; NULL: every token), as
+   `_seen_rows[row]` holds them; next[i] = sampled[i, accepted[i]], the token the next step runs;
+   row[i] = i * (drafts + 1) + accepted[i], the row whose hidden state the slot keeps. */
+int leat_settle_draft(const int32_t* accepted, const int32_t* last, const int32_t* drafted, const int32_t* sampled,
+                      const int32_t* slots, int32_t n, int32_t drafts, int32_t* history_ids, int32_t* history_count,
+                      int32_t capacity, const uint8_t* text, int32_t vocab, int32_t* next, int32_t* row,
                       leat_stream_t stream);
 
 /* Vocabulary shards (no reference counterpart: leat runs one model per GPU, leat/server.py:427-428).

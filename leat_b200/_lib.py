@@ -27,7 +27,7 @@ EXPORTS = [
     "leat_sampler_tune", "leat_sampler_tune_filter", "leat_sampler_tune_ring", "leat_sampler_plan", "leat_sampler_last_launches",
     "leat_sampler_time_kernels", "leat_sampler_kernel_times",
     "leat_sampler_last_cuda_error", "leat_sample", "leat_argmax", "leat_cutoff",
-    "leat_verify_draft", "leat_topk_local", "leat_sample_from_candidates", "leat_sample_static",
+    "leat_verify_draft", "leat_settle_draft", "leat_topk_local", "leat_sample_from_candidates", "leat_sample_static",
     "leat_candidate_record_bytes", "leat_candidate_record_layout", "leat_sample_from_records",
     "leat_shard_region_bytes", "leat_peer_alloc", "leat_peer_open", "leat_peer_close", "leat_peer_free",
     "leat_shard_create", "leat_shard_destroy", "leat_shard_select", "leat_shard_finish", "leat_shard_result",
@@ -50,6 +50,7 @@ class SampleArgs(C.Structure):
         ("out_ids", C.c_void_p), ("out_greedy", C.c_void_p), ("out_cut", C.c_void_p),
         ("out_kept", C.c_void_p), ("out_probs", C.c_void_p), ("out_prob_ids", C.c_void_p),
         ("out_width", C.c_int32), ("status", C.c_void_p),
+        ("softcap", C.c_float), ("position_scalar", C.c_int32),
     ]  # fmt: skip
 
 
@@ -83,6 +84,7 @@ def _load() -> C.CDLL:
     lib.leat_argmax.argtypes = [p, p, i32, i32, i64, p, p, p]
     lib.leat_cutoff.argtypes = [p, p, i32, i32, i64, p, p, p, p, p, p]
     lib.leat_verify_draft.argtypes = [p, p, p, i32, i32, p, p, p]
+    lib.leat_settle_draft.argtypes = [p, p, p, p, p, i32, i32, p, p, i32, p, i32, p, p, p]
     lib.leat_topk_local.argtypes = [p, C.POINTER(SampleArgs), p, p, p, p, i32, p]
     lib.leat_sample_from_candidates.argtypes = [p, C.POINTER(SampleArgs), p, p, p, p, i32, i32, p]
     lib.leat_candidate_record_bytes.restype = sz

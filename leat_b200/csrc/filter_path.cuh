@@ -243,8 +243,10 @@ __device__ __forceinline__ void sample_maxima(const void* row, int V, int vecs, 
 }
 
 // The row's floor from its sorted sample maxima: +inf for rows that do not use a list (whole-row
-// Gumbel rows, rows for the multi-pass routine and rows whose list would be long).
-__device__ __forceinline__ float floor_from_sample(const RowCfg& rc, int V, int sample, int list_cap, const float* sorted) {
+// Gumbel rows, rows for the multi-pass routine and rows whose list would be long; under a soft cap
+// also min-p rows, whose threshold lives in capped scores while the floor is a raw logit).
+__device__ __forceinline__ float floor_from_sample(const RowCfg& rc, int V, int sample, int list_cap, const float* sorted,
+                                                   bool capped) {
   const int mode = rc.mode;
   float floor_l = pos_inf();
   if (mode == M_SELECT_K) {
@@ -253,7 +255,7 @@ __device__ __forceinline__ float floor_from_sample(const RowCfg& rc, int V, int 
     if (j <= SAMPLE_MAX_ORDER && (long long)j * V / sample * 4 <= (long long)list_cap * 3) floor_l = sorted[j - 1];
   } else if (mode == M_ARGMAX_L) {
     floor_l = sorted[3];
-  } else if (mode == M_SELECT_MINP) {
+  } else if (mode == M_SELECT_MINP && !capped) {
     // survivors score at least (true top) + log(min_p), and the true top is at least the sample's
     const float f = logit_floor(scaled(sorted[0], rc) + rc.logm, rc.tf);
     if (f >= sorted[SAMPLE_MAX_ORDER - 1]) floor_l = f;
@@ -286,7 +288,7 @@ __device__ __forceinline__ float block_floor(const KParams& P, int b, unsigned l
   const unsigned char* row = reinterpret_cast<const unsigned char*>(P.logits) + (size_t)b * P.row_stride * (16 / T::PER_VEC);
   const int vecs = sample_vecs(P.vocab, T::PER_VEC);
   sample_maxima<T>(row, P.vocab, vecs, runs, sorted);
-  const float floor_l = floor_from_sample(*rc, P.vocab, SAMPLE_CHUNKS * vecs * T::PER_VEC, P.list_cap, sorted);
+  const float floor_l = floor_from_sample(*rc, P.vocab, SAMPLE_CHUNKS * vecs * T::PER_VEC, P.list_cap, sorted, P.softcap > 0.0f);
   if (tid == 0)
     P.list_info[b] = INFO_READY | (lean_takes(P, *rc, floor_l) ? INFO_LEAN : 0ull) | (unsigned long long)__float_as_uint(floor_l);
   return floor_l;

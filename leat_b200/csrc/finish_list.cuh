@@ -467,7 +467,7 @@ __device__ __forceinline__ void finish_list_block(const KParams& P, unsigned cha
   for (int q = 0; q < PRE; ++q) pre[q] = __ldcg(&list[q * NT + tid]);
   __syncthreads();  // the history marks are in; every thread has the list's length
   const bool lean = (info & INFO_LEAN) != 0ull;
-  const float floor_l = info_floor(info);
+  const float floor_l = soft_capped(info_floor(info), P.softcap);  // (what a logit under the floor is at most, capped)
   // the next call's filter must find the row's list empty and its word unmarked
   if (tid == 0) {
     P.list_info[b] = info & ~INFO_READY;
@@ -486,7 +486,7 @@ __device__ __forceinline__ void finish_list_block(const KParams& P, unsigned cha
     int live = 0;
     auto visit = [&](int i, unsigned long long pair) {
       const int idx = (int)(uint32_t)pair;
-      float l = __uint_as_float((uint32_t)(pair >> 32));
+      float l = soft_capped(__uint_as_float((uint32_t)(pair >> 32)), P.softcap);
       if (P.history) {
         const int count = bitmap ? (int)((area[idx >> 5] >> (idx & 31)) & 1u) : fl_count(hkeys, hcnt, ht - 1, idx);
         if (count) l = penalised(l, count, rc);
@@ -521,7 +521,10 @@ __device__ __forceinline__ void finish_list_block(const KParams& P, unsigned cha
   }
   __syncthreads();  // keys are in; the history marks are dead, their area is free
   // a greedy token is only known if the best candidate reaches the floor (nothing dropped beats it)
-  if (rc.track && !(S.gbest != 0ull && key_value(S.gbest) >= floor_l)) failed = true;
+  // (under a soft cap it must beat the floor: distinct logits may be capped to the same float, and
+  // the first index wins a tie)
+  if (rc.track && !(S.gbest != 0ull && (P.softcap > 0.0f ? key_value(S.gbest) > floor_l : key_value(S.gbest) >= floor_l)))
+    failed = true;
   if (tid == 0 && P.out_greedy) P.out_greedy[b] = key_id(S.gbest);
   unsigned long long* cbuf = reinterpret_cast<unsigned long long*>(area);
   unsigned long long* runs = cbuf + FL_SORT;

@@ -42,7 +42,7 @@ struct GRow {
 
 // score of token i (penalties, temperature) and whether it counts (NaN scores do not)
 __device__ __forceinline__ bool g_score(const GRow& g, int i, float& l_out, float& s_out) {
-  float l = logit_at(*g.P, g.b, i);
+  float l = soft_capped(logit_at(*g.P, g.b, i), g.P->softcap);
   int count = g.P->history ? history_count(g.h, i) : 0;
   if (g.seen_row && g.seen_row[i]) count = max(count, 1);
   if (count) l = penalised(l, count, *g.rc);

@@ -7,6 +7,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
 #include <new>
 
 #include "sampler_kernels.cuh"
@@ -205,6 +206,8 @@ int fill_params(const leat_sampler* h, const leat_sample_args* a, KParams& P) {
   P.penalties = a->penalties; P.penalties_rows = a->penalties_rows;
   P.uniform = a->uniform;
   P.vocab_offset = a->vocab_offset; P.flags = a->flags;
+  if (!(a->softcap >= 0.0f)) return LEAT_E_ARGUMENT;
+  P.softcap = a->softcap; P.position_scalar = a->position_scalar;
   if ((a->flags & LEAT_FLAG_LOGITS_BF16) && (a->flags & LEAT_FLAG_LOGITS_F16)) return LEAT_E_ARGUMENT;
   P.dtype = (a->flags & LEAT_FLAG_LOGITS_BF16) ? 1 : ((a->flags & LEAT_FLAG_LOGITS_F16) ? 2 : 0);
   P.out_ids = a->out_ids; P.out_greedy = a->out_greedy; P.out_cut = a->out_cut; P.out_kept = a->out_kept;
@@ -541,12 +544,26 @@ int leat_verify_draft(const int32_t* drafted, const int32_t* sampled, const int3
   return cuda_failed(cudaGetLastError(), "verify_kernel launch") ? LEAT_E_CUDA : LEAT_OK;
 }
 
+int leat_settle_draft(const int32_t* accepted, const int32_t* last, const int32_t* drafted, const int32_t* sampled,
+                      const int32_t* slots, int32_t n, int32_t drafts, int32_t* history_ids, int32_t* history_count,
+                      int32_t capacity, const uint8_t* text, int32_t vocab, int32_t* next, int32_t* row,
+                      leat_stream_t stream) {
+  if (!accepted || !last || !sampled || !history_ids || !history_count || n < 0 || drafts < 0 || capacity <= 0 ||
+      vocab <= 0 || (drafts > 0 && !drafted))
+    return LEAT_E_ARGUMENT;
+  if (n == 0) return LEAT_OK;
+  settle_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      accepted, last, drafted, sampled, slots, n, drafts, history_ids, history_count, capacity, text, vocab, next, row);
+  return cuda_failed(cudaGetLastError(), "settle_kernel launch") ? LEAT_E_CUDA : LEAT_OK;
+}
+
 int leat_topk_local(leat_sampler_t* h, const leat_sample_args* a, float* cand_value, int32_t* cand_id,
                     int32_t* cand_count, uint64_t* best, int32_t cap, leat_stream_t stream) {
   if (!cand_value || !cand_id || !cand_count || !best || cap <= 0) return LEAT_E_ARGUMENT;
   KParams P;
   int rc = fill_params(h, a, P);
   if (rc != LEAT_OK) return rc;
+  if (a->softcap > 0.0f) return LEAT_E_ARGUMENT;  // (a soft cap goes with the list finish: use leat_shard_select)
   P.cand_value = cand_value; P.cand_id = cand_id; P.cand_count = cand_count;
   P.cand_best = reinterpret_cast<unsigned long long*>(best); P.cand_cap = cap;
   return launch_sample(h, P, static_cast<cudaStream_t>(stream));
@@ -657,12 +674,14 @@ struct StaticDevice {
   leat_sampler handle;
 };
 StaticDevice g_static_devices[64];
+std::mutex g_static_lock;  // the first call on a device sets its entry up; threads may race to it
 
 // Once per device, with that device current: the array's name is only a host-side stand-in, so
 // ask the runtime for the device address kernels can use.
 int static_setup(int device, StaticDevice** out) {
   if (device < 0 || device >= 64) return LEAT_E_DEVICE;
   StaticDevice& sd = g_static_devices[device];
+  std::lock_guard<std::mutex> guard(g_static_lock);
   if (!sd.ready) {
     void* scratch = nullptr;
     if (cuda_failed(cudaGetSymbolAddress(&scratch, g_static_scratch), "cudaGetSymbolAddress")) return LEAT_E_CUDA;
@@ -702,6 +721,13 @@ int static_setup(int device, StaticDevice** out) {
 int leat_sample_static(const leat_sample_args* a, leat_stream_t stream) {
   if (!a || !a->out_ids) return LEAT_E_ARGUMENT;
   if (a->rows > kStaticRows || a->vocab > kStaticVocab) return LEAT_E_CAPACITY;
+  if (a->rows == 0) {  // nothing to sample; the status word is still cleared on request, as leat_sample does
+    if (a->vocab <= 0) return LEAT_E_ARGUMENT;
+    if ((a->flags & LEAT_FLAG_CLEAR_STATUS) && a->status &&
+        cuda_failed(cudaMemsetAsync(a->status, 0, sizeof(int), static_cast<cudaStream_t>(stream)), "cudaMemsetAsync"))
+      return LEAT_E_CUDA;
+    return LEAT_OK;
+  }
   int device = -1;
   if (cuda_failed(cudaGetDevice(&device), "cudaGetDevice")) return LEAT_E_CUDA;
   StaticDevice* sd = nullptr;

@@ -54,6 +54,8 @@ struct KParams {
   const float* penalties; int penalties_rows;
   const float* uniform;
   int vocab_offset; unsigned flags; int force_greedy;
+  float softcap;        // the model's soft cap on its logits (0: none)
+  int position_scalar;  // every row's position when `position` is null
   int* out_ids; int* out_greedy; float* out_cut; int* out_kept;
   float* out_probs; int* out_prob_ids; int out_width; int* status;
   // shard mode: publish the row's candidates instead of finishing it
@@ -148,6 +150,13 @@ __device__ __forceinline__ float penalised(float l, int count, const RowCfg& rc)
   return r - off;
 }
 
+// the model's soft cap, tanh(l / cap) * cap (leat/model.py:419-423), in double precision and rounded
+// once, so that the CPU statement of it gives the same float; monotone, so a raw logit under a
+// row's floor is, capped, at or under the capped floor
+__device__ __forceinline__ float soft_capped(float l, float cap) {
+  return cap > 0.0f ? (float)(tanh((double)l / (double)cap) * (double)cap) : l;
+}
+
 __device__ __forceinline__ float scaled(float l, const RowCfg& rc) {
   return rc.divide ? l / rc.tf : l * rc.rinv;
 }
@@ -183,7 +192,7 @@ __device__ inline RowIn row_inputs(const KParams& P, int b) {
   }
   in.u = P.uniform ? P.uniform[b] : 0.0f;
   in.seed = P.seed ? P.seed[P.seed_rows == 1 ? 0 : b] : 0u;
-  in.pos = P.position ? P.position[P.position_rows == 1 ? 0 : b] : 0;
+  in.pos = P.position ? P.position[P.position_rows == 1 ? 0 : b] : P.position_scalar;
   return in;
 }
 
@@ -227,7 +236,7 @@ __device__ inline RowIn row_inputs_warp(const KParams& P, int b, const void* ext
   if (P.penalties) { in.rep = __uint_as_float(v[5]); in.pres = __uint_as_float(v[6]); in.freq = __uint_as_float(v[7]); }
   in.u = __uint_as_float(v[8]);
   in.seed = v[9];
-  in.pos = (int)v[10];
+  in.pos = P.position ? (int)v[10] : P.position_scalar;
   extra_out = v[11];
   return in;
 }
@@ -868,7 +877,11 @@ __device__ __noinline__ void slice_history(const KParams& P, const RowCfg& rc, c
         }
         if (!__syncthreads_or(pending != 0u)) break;
         buffer_rebuild(c, 0);
-        if (sm.overflow || ++rounds > 64) break;
+        if (sm.overflow || ++rounds > 64) {  // entries still pending: the row is not settled here
+          if (tid == 0) sm.overflow = 1;
+          __syncthreads();
+          break;
+        }
 #pragma unroll
         for (int j = 0; j < HB; ++j)
           if (((pending >> j) & 1u) && !(key_value(keys[j]) >= sm.tau)) pending &= ~(1u << j);
@@ -1061,6 +1074,8 @@ __device__ __forceinline__ void sample_block(const KParams& P, const int b, cons
     sm.floor_l = P.list ? __uint_as_float(floor_bits) : __uint_as_float(0x7F800000u);
     // the streaming code reads float32 only: a 16-bit row without a list is left to the multi-pass routine
     if (P.dtype != 0 && !(sm.floor_l < __uint_as_float(0x7F800000u))) { rc.mode = M_GENERAL; c.mode = M_GENERAL; }
+    // a soft cap is applied where candidates are few: here, by the multi-pass routine
+    if (P.softcap > 0.0f) { rc.mode = M_GENERAL; c.mode = M_GENERAL; }
     sm.s_floor = neg_inf();
     if (sm.floor_l < __uint_as_float(0x7F800000u)) {
       // nothing scoring under the floor can matter to a row whose list stands
@@ -1535,6 +1550,30 @@ __global__ void verify_kernel(const int* __restrict__ drafted, const int* __rest
     else if (j == kept) t = sampled[(size_t)i * ran + j];
     tokens[(size_t)i * ran + j] = t;
   }
+}
+
+
+// leat/engine.py:677-686 with the history kept as ids: one thread per sequence
+__global__ void settle_kernel(const int* __restrict__ accepted, const int* __restrict__ last, const int* __restrict__ drafted,
+                              const int* __restrict__ sampled, const int* __restrict__ slots, int n, int drafts,
+                              int* history_ids, int* history_count, int capacity, const uint8_t* __restrict__ text,
+                              int vocab, int* next, int* row) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int ran = drafts + 1;
+  const int kept = min(max(accepted[i], 0), drafts);
+  const int slot = slots ? slots[i] : i;
+  int count = history_count[slot];
+#pragma unroll 1
+  for (int j = 0; j <= kept; ++j) {
+    const int token = j == 0 ? last[i] : drafted[(size_t)i * drafts + j - 1];
+    if (token < 0 || token >= vocab || (text && !text[token])) continue;
+    history_ids[(size_t)slot * capacity + count % capacity] = token;
+    count += 1;
+  }
+  history_count[slot] = count;
+  if (next) next[i] = sampled[(size_t)i * ran + kept];
+  if (row) row[i] = i * ran + kept;
 }
 
 }  // namespace leat

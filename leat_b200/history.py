@@ -94,11 +94,64 @@ def dense_mask(ids: torch.Tensor, vocab: int, length: torch.Tensor | None = None
     return mask[:, :vocab].contiguous()
 
 
+# what each option must be, as leat's server and defaults state it (leat/server.py:84-109: temperature
+# 0..2, top_k an integer, top_p and min_p 0..1, presence_penalty -2..2; leat/defaults.py:26-29: top_k up
+# to 2^20), and the ranges this sampler gives the two penalties leat's server refuses outright
+# (leat/server.py:112-115): OpenAI's -2..2 for frequency_penalty, (0, 2] for repetition_penalty
+BOUNDS = {
+    "temperature": (0.0, 2.0), "top_k": (0, 1 << 20), "top_p": (0.0, 1.0), "min_p": (0.0, 1.0),
+    "presence_penalty": (-2.0, 2.0), "frequency_penalty": (-2.0, 2.0), "repetition_penalty": (0.0, 2.0),
+}  # fmt: skip
+
+
+def _number(name: str, value, integer: bool = False) -> float:
+    if isinstance(value, bool) or not isinstance(value, (int, float)) or value != value:
+        raise ValueError(f"{name} must be {'an integer' if integer else 'a number'}")
+    if integer and int(value) != value:
+        raise ValueError(f"{name} must be an integer")
+    return value
+
+
+def sampling_from_request(body: dict, defaults: dict | None = None):
+    """A request's sampling fields as a `Sampling` plus the two extra penalties, checked as leat's
+    server checks them (leat/server.py:84-109, :921-924): a field that is absent or None takes the
+    default (OpenAI's, leat/defaults.py:31, unless `defaults` says otherwise), a top_k of -1 (vLLM's
+    "every token") becomes 0, and a value outside its range raises ValueError.  Returns
+    (Sampling, frequency_penalty, repetition_penalty)."""
+    from leat_b200.sampler import Sampling
+
+    base = {"temperature": 1.0, "top_k": 0, "top_p": 1.0, "min_p": 0.0, "presence_penalty": 0.0}
+    base.update(defaults or {})
+    given = {k: v for k, v in body.items() if v is not None}
+    values = {}
+    for name in ("temperature", "top_k", "top_p", "min_p", "presence_penalty"):
+        value = _number(name, given.get(name, base[name]), integer=name == "top_k")
+        if name == "top_k":
+            value = max(int(value), 0)  # vLLM's -1: every one
+        low, high = BOUNDS[name]
+        if not low <= value <= high:
+            raise ValueError(f"{name} must be a number from {low} to {high}")
+        values[name] = value
+    frequency = _number("frequency_penalty", given.get("frequency_penalty", 0.0))
+    repetition = _number("repetition_penalty", given.get("repetition_penalty", 1.0))
+    if not BOUNDS["frequency_penalty"][0] <= frequency <= BOUNDS["frequency_penalty"][1]:
+        raise ValueError("frequency_penalty must be a number from -2 to 2")
+    if not 0.0 < repetition <= BOUNDS["repetition_penalty"][1]:
+        raise ValueError("repetition_penalty must be a number above 0, up to 2")
+    return Sampling(float(values["temperature"]), int(values["top_k"]), float(values["top_p"]), float(values["min_p"]),
+                    float(values["presence_penalty"])), float(frequency), float(repetition)  # fmt: skip
+
+
 def options_row(sampling, frequency_penalty: float = 0.0, repetition_penalty: float = 1.0) -> tuple[list[float], list[float]]:
     """A request's sampling settings as the two rows the sampler reads: options
     (temperature, top_k, top_p, min_p, presence_penalty), as `Sampling.values()` lays them out
     (leat/sampler.py:17-25, used at leat/engine.py:569), and penalties (repetition, presence,
     frequency), which also carries the two penalties leat's server refuses today
-    (leat/server.py:84-115)."""
+    (leat/server.py:84-115).  Values outside the ranges leat's server and defaults allow
+    (`BOUNDS`) raise ValueError: the kernels themselves check nothing, as leat's sampler does not."""
+    sampling, frequency_penalty, repetition_penalty = sampling_from_request(
+        {"temperature": sampling.temperature, "top_k": sampling.top_k, "top_p": sampling.top_p, "min_p": sampling.min_p,
+         "presence_penalty": sampling.presence_penalty, "frequency_penalty": frequency_penalty,
+         "repetition_penalty": repetition_penalty})  # fmt: skip
     options = [float(v) for v in sampling.values()]
     return options, [float(repetition_penalty), float(sampling.presence_penalty), float(frequency_penalty)]

@@ -60,6 +60,21 @@ def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+def device_tensor(x):
+    """`x` as a torch tensor without copying: torch tensors as they are, any other framework's device
+    buffer through DLPack (`__dlpack__`) or the CUDA array interface (`__cuda_array_interface__`:
+    numba, CuPy, a tinygrad buffer wrapped in either), so that leat's own tensors can be handed to
+    sample() where it keeps them.  Anything else (lists, NumPy arrays) is left to the caller's
+    conversion.  The results are torch tensors, which export both protocols in turn."""
+    if x is None or isinstance(x, torch.Tensor):
+        return x
+    if hasattr(x, "__cuda_array_interface__"):
+        return torch.as_tensor(x, device="cuda")
+    if hasattr(x, "__dlpack__"):
+        return torch.from_dlpack(x)
+    return x
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -130,7 +145,11 @@ class Sampler:
     # ---- argument marshalling -------------------------------------------------------------------
 
     def _args(self, logits, options, seed, position, seen, history, history_len, penalties, uniform,
-              flags, vocab_offset=0, vocab_total=0) -> tuple[_lib.SampleArgs, list]:  # fmt: skip
+              flags, vocab_offset=0, vocab_total=0, softcap: float = 0.0) -> tuple[_lib.SampleArgs, list]:  # fmt: skip
+        logits, options, seed, seen = device_tensor(logits), device_tensor(options), device_tensor(seed), device_tensor(seen)
+        history, history_len, penalties = device_tensor(history), device_tensor(history_len), device_tensor(penalties)
+        uniform = device_tensor(uniform)
+        position = position if isinstance(position, int) else device_tensor(position)
         formats = {torch.float32: 0, torch.bfloat16: _lib.FLAG_LOGITS_BF16, torch.float16: _lib.FLAG_LOGITS_F16}
         if logits.dim() != 2 or logits.dtype not in formats or not logits.is_cuda:
             raise ValueError("logits must be a (B, V) float32, bfloat16 or float16 CUDA tensor")
@@ -156,7 +175,9 @@ class Sampler:
 
         options, options_rows = tensor(options, torch.float32, 5, "options")
         seed, seed_rows = tensor(seed, torch.uint32 if hasattr(torch, "uint32") else torch.int32, None, "seed")
-        position, position_rows = tensor(position, torch.int32, None, "position")
+        # an int position goes by value (leat's graph variable, leat/sampler.py:41-42): no copy, no tensor
+        scalar_position = position if isinstance(position, int) and not isinstance(position, bool) else None
+        position, position_rows = tensor(None if scalar_position is not None else position, torch.int32, None, "position")
         penalties, penalties_rows = tensor(penalties, torch.float32, 3, "penalties")
         a = _lib.SampleArgs()
         a.logits, a.rows, a.vocab, a.row_stride = logits.data_ptr(), rows, vocab, logits.stride(0)
@@ -195,6 +216,7 @@ class Sampler:
             keep.append(uniform)
             a.uniform = uniform.data_ptr()
         a.vocab_offset, a.vocab_total, a.flags = vocab_offset, vocab_total, flags | _lib.FLAG_CLEAR_STATUS
+        a.softcap, a.position_scalar = float(softcap), int(scalar_position or 0)
         return a, keep
 
     # ---- entry points ---------------------------------------------------------------------------
@@ -203,10 +225,11 @@ class Sampler:
         self, logits: torch.Tensor, options, seed=None, position=0, seen=None, *,
         history=None, history_len=None, penalties=None, uniform=None, width: int = 0,
         want_greedy: bool = False, want_cut: bool = False, flags: int = 0, out: torch.Tensor | None = None,
+        softcap: float = 0.0,
     ) -> Sampled:  # fmt: skip
         a, keep = self._args(logits, options, seed, position, seen, history, history_len, penalties,
-                             uniform, flags)  # fmt: skip
-        rows, dev = a.rows, logits.device
+                             uniform, flags, softcap=softcap)  # fmt: skip
+        rows, dev = a.rows, keep[0].device
         ids = out if out is not None else torch.empty((rows, 1), dtype=torch.int32, device=dev)
         result = Sampled(ids, status=torch.empty(1, dtype=torch.int32, device=dev))  # cleared by the call (FLAG_CLEAR_STATUS)
         a.out_ids, a.status = ids.data_ptr(), result.status.data_ptr()
@@ -283,7 +306,7 @@ def sample_static(logits: torch.Tensor, options, seed=None, position=0, seen=Non
     allocates nothing.)"""
     a, keep = Sampler._args(None, logits, options, seed, position, seen, history, history_len, penalties,
                             uniform, flags)  # fmt: skip
-    rows, dev = a.rows, logits.device
+    rows, dev = a.rows, keep[0].device
     ids = out if out is not None else torch.empty((rows, 1), dtype=torch.int32, device=dev)
     result = Sampled(ids, status=torch.empty(1, dtype=torch.int32, device=dev))  # cleared by the call (FLAG_CLEAR_STATUS)
     a.out_ids, a.status = ids.data_ptr(), result.status.data_ptr()
@@ -308,5 +331,6 @@ def sample(logits: torch.Tensor, options: torch.Tensor, seed: torch.Tensor, posi
     """leat/sampler.py:31-55: picks one token per row of `logits` (B, V), as its options say;
     returns (B, 1) int32 on the device.  A row's draw depends only on its logits, its options, its
     seed and its position."""
+    logits = device_tensor(logits)  # (any framework's device buffer: DLPack or the CUDA array interface)
     sampler = default_sampler(logits.shape[0], logits.shape[1], logits.device)
     return sampler.sample(logits, options, seed, position, seen, **extensions)

@@ -156,6 +156,18 @@ def penalise(logits, counts, repetition, presence, frequency):
         return np.where(hit, (rep - off).astype(F32), l).astype(F32)
 
 
+def soft_cap(logits, cap):
+    """leat/model.py:419-423: logits = tanh(logits / cap) * cap, the soft cap a model puts on its
+    logits before they are sampled (cap 0 or None: none).  The reference evaluates it in float32
+    through tinygrad, which cannot be run here (PARITY UNPINNED); the convention fixed here and in the
+    CUDA path is double precision rounded once to float32, which both sides reproduce exactly."""
+    l = np.asarray(logits, F32)
+    if not cap:
+        return l
+    with np.errstate(invalid="ignore", over="ignore"):
+        return (np.tanh(l.astype(np.float64) / np.float64(F32(cap))) * np.float64(F32(cap))).astype(F32)
+
+
 def scale_scores(l, temperature, scale: str = "reciprocal"):
     """leat/sampler.py:50: scores = logits / max(T, 1e-6)."""
     t = np.maximum(F32(temperature), T_FLOOR)
@@ -245,6 +257,7 @@ class Result:
     probs: list = field(default_factory=list)  # per row: their probabilities
     margin: np.ndarray | None = None  # (B,) smallest relative distance of a decision from flipping
     penalised: np.ndarray | None = None  # (B, V) penalised logits, when asked for
+    notes: dict = field(default_factory=dict)  # row -> nucleus_boundary() of a row whose margin is under 1e-5
 
 
 def _rows(x, rows, width=None, dtype=None):
@@ -258,7 +271,7 @@ def sample(
     logits, options, seed=None, position=0, seen=None, *,
     history=None, history_len=None, penalties=None, uniform_draws=None,
     scale: str = "reciprocal", order: str = "sequential", survivors: bool = True,
-    keep_penalised: bool = False, vocab_start: int = 0,
+    keep_penalised: bool = False, vocab_start: int = 0, softcap: float = 0.0,
 ) -> Result:  # fmt: skip
     """leat/sampler.py:31-55 for float32 `logits` (B, V) and `options` (B|1, 5) rows of
     [temperature, top_k, top_p, min_p, presence_penalty].
@@ -268,11 +281,12 @@ def sample(
 
     Extensions: `history` (B, H) int32 with `history_len` (B,) gives per-token counts (a `seen`
     mask counts as one occurrence where the history has none); `penalties` (B|1, 3) rows of
-    [repetition, presence, frequency] replace the options' presence column; `uniform_draws` (B,)
+    [repetition, presence, frequency] replace the options' presence column; `softcap` applies the
+    model's soft cap (soft_cap) to the logits first; `uniform_draws` (B,)
     switches the draw to inverse-CDF: survivors ordered by descending score, ties by ascending id,
     weights exp(score - top), the first survivor whose running weight exceeds u * total, else the
     last.  `vocab_start` offsets the hashed index (a vocabulary shard)."""
-    logits = np.asarray(logits, F32)
+    logits = soft_cap(np.asarray(logits, F32), softcap)  # (the model's own last step, before any penalty)
     rows, vocab = logits.shape
     options = _rows(options, rows, 5, F32)
     counts = None
@@ -333,6 +347,8 @@ def sample(
             out.ids[b, 0] = int(by_rank[j]) + vocab_start
             margin = min(margin, float(np.min(np.abs(incl - bound)) / total))
         out.margin[b] = margin
+        if margin < 1e-5 and temperature > 0:
+            out.notes[b] = nucleus_boundary(s, top_k, top_p)
     return out
 
 
@@ -375,6 +391,43 @@ def verify_draft_greedy(drafted, greedy, sampled):
         tokens[i, : kept[i]] = drafted[i, : kept[i]]
         tokens[i, kept[i]] = sampled[i, kept[i]]
     return kept, tokens
+
+
+def settle_draft(ids, count, capacity, text, slots, last, drafted, sampled, accepted):
+    """What leat does after the accept loop (leat/engine.py:609-631, `_settled` :677-686), with each
+    slot's generated tokens kept as a ring of ids (ids (slots, capacity), count (slots,)) instead of
+    the dense `_seen` mask: the slot takes the tokens that were run up to the kept row, last[i] then
+    drafted[i, :accepted[i]], except markup (`text[token]` false); next[i] = sampled[i, accepted[i]];
+    row[i] = i * (drafts + 1) + accepted[i].  Updates ids and count in place."""
+    n, ran = np.asarray(sampled).shape
+    nxt, row = np.zeros(n, np.int32), np.zeros(n, np.int32)
+    for i in range(n):
+        kept = int(accepted[i])
+        for token in [int(last[i]), *[int(t) for t in drafted[i][:kept]]]:
+            if 0 <= token < len(text) and text[token]:
+                ids[slots[i], count[slots[i]] % capacity] = token
+                count[slots[i]] += 1
+        nxt[i], row[i] = sampled[i][kept], i * ran + kept
+    return nxt, row
+
+
+def nucleus_boundary(scores, top_k, top_p):
+    """For a row whose draw hangs on a top-p comparison: the rank at which the likelier mass comes
+    closest to top_p * kept, with that mass and that bound in both summation orders, for the log of
+    rows exempted as nucleus-boundary ties."""
+    ranked = -np.sort(-np.asarray(scores, F32))
+    n = len(ranked)
+    in_k = int(min(math.floor(float(top_k)) if top_k > 0 else n, n))
+    with np.errstate(invalid="ignore", over="ignore"):
+        weights = exp32(ranked[:in_k] - ranked[0])
+    out = {}
+    for order in ("sequential", "block"):
+        incl = running_sum(weights, order)
+        likelier = (incl - weights).astype(F32)
+        bound = F32(F32(top_p) * incl[-1])
+        j = int(np.argmin(np.abs(likelier[1:] - bound))) + 1 if in_k > 1 else 0
+        out[order] = {"rank": j, "likelier": float(likelier[j]), "top_p_times_kept": float(bound)}
+    return out
 
 
 # ----------------------------------------------------------------------------------------------

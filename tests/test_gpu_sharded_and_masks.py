@@ -207,6 +207,16 @@ def test_sparse_slot_history_equals_the_dense_mask(device):
     dense = sampler.sample_full(t(logits), t(options), seed, position, seen.to(torch.uint8), uniform=uniform, width=40,
                                 want_greedy=True, want_cut=True)  # fmt: skip
     torch.cuda.synchronize()
+    # each against the CPU oracle given the same tokens (as ids and as the mask), then one against the other
+    from oracle import sampler_oracle as oracle
+
+    hist, lens = history.cpu().numpy(), length.cpu().numpy()
+    want = oracle.sample(logits, options, np.arange(rows), 7, history=hist, history_len=lens,
+                         penalties=np.tile(np.array([1.0, 1.5, 0.0], np.float32), (rows, 1)),
+                         uniform_draws=uniform.cpu().numpy(), order="block")  # fmt: skip
+    helpers.compare(want, sparse, 40, max_fragile=0)
+    want_dense = oracle.sample(logits, options, np.arange(rows), 7, seen.cpu().numpy(), uniform_draws=uniform.cpu().numpy(), order="block")
+    helpers.compare(want_dense, dense, 40, max_fragile=0)
     for name in ("ids", "greedy", "kept", "cut", "prob_ids", "probs"):
         a, b = getattr(sparse, name).cpu().numpy(), getattr(dense, name).cpu().numpy()
         if name == "cut":

@@ -71,3 +71,32 @@ def test_request_to_option_rows():
 
     options, penalties = options_row(Sampling(0.7, 40, 0.9, 0.05, 0.5), frequency_penalty=0.2, repetition_penalty=1.1)
     assert options == [0.7, 40.0, 0.9, 0.05, 0.5] and penalties == [1.1, 0.5, 0.2]
+
+
+def test_request_mapping_follows_the_reference_server():
+    """leat's own mapping cases (tests/test_server.py:255-266 of the reference): OpenAI's fields and
+    vLLM's, top_k of -1 keeping every token as 0; absent or null fields take OpenAI's defaults."""
+    import pytest
+
+    from leat_b200.history import sampling_from_request
+    from leat_b200.sampler import Sampling
+
+    body = {"temperature": 0.5, "top_k": -1, "top_p": 0.9, "min_p": 0.05, "presence_penalty": 1.5, "max_tokens": 9, "seed": 3}
+    sampling, frequency, repetition = sampling_from_request(body)
+    assert sampling == Sampling(0.5, 0, 0.9, 0.05, 1.5) and (frequency, repetition) == (0.0, 1.0)
+    sampling, _, _ = sampling_from_request({"stop": ["", "y"], "top_p": None})
+    assert sampling == Sampling(1.0)
+    # a model's own defaults, which a request's fields override (leat/defaults.py)
+    sampling, _, _ = sampling_from_request({"top_k": 20}, defaults={"temperature": 0.6, "top_k": 40, "top_p": 0.95})
+    assert sampling == Sampling(0.6, 20, 0.95)
+    # the ranges of leat/server.py:84-109 and leat/defaults.py:26-29
+    for bad in ({"temperature": 2.5}, {"temperature": -0.1}, {"top_p": 1.2}, {"min_p": -0.5}, {"presence_penalty": 3},
+                {"top_k": 1.5}, {"top_k": (1 << 20) + 1}, {"temperature": "hot"}, {"top_p": True},
+                {"frequency_penalty": 2.5}, {"repetition_penalty": 0}, {"repetition_penalty": 2.5}):  # fmt: skip
+        with pytest.raises(ValueError):
+            sampling_from_request(bad)
+    # the two penalties leat's server refuses are taken here
+    _, frequency, repetition = sampling_from_request({"frequency_penalty": 0.4, "repetition_penalty": 1.2})
+    assert (frequency, repetition) == (0.4, 1.2)
+    with pytest.raises(ValueError):
+        options_row(Sampling(3.0))

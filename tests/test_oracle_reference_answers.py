@@ -93,6 +93,31 @@ def test_hashed_uniform_is_a_23_bit_grid_inside_the_unit_interval():
                                   np.array([0.82124513, 0.46080738, 0.9425561, 0.3054096], np.float32))  # fmt: skip
 
 
+def test_hash_is_the_published_lowbias32():
+    """leat's `_hash` (leat/sampler.py:67-73) is hash-prospector's lowbias32, a bijection of 32-bit
+    words whose author also publishes its inverse (multipliers 0x43021123 and 0x1d69e2a5 with the
+    shifts undone).  The published inverse, written out here independently, must take the hash back
+    to its input, and its multipliers must be the forward ones' inverses modulo 2^32: that pins the
+    restatement to the published function, not to itself."""
+    assert (0x846CA68B * 0x43021123) % 2**32 == 1 and (0x7FEB352D * 0x1D69E2A5) % 2**32 == 1
+
+    def inverse(x: int) -> int:
+        x ^= x >> 16
+        x = (x * 0x43021123) % 2**32
+        x ^= (x >> 15) ^ (x >> 30)
+        x = (x * 0x1D69E2A5) % 2**32
+        x ^= x >> 16
+        return x
+
+    rng = np.random.default_rng(5)
+    words = np.concatenate([np.array([0, 1, 2, 0xFFFFFFFF, 0x80000000, 0x7FFFFFFF], np.uint64),
+                            rng.integers(0, 2**32, 2000, dtype=np.uint64)]).astype(np.uint32)  # fmt: skip
+    hashed = oracle.lowbias32(words)
+    assert hashed.dtype == np.uint32 and oracle.lowbias32(0)[0] == 0  # (zero is the hash's fixed point)
+    assert [inverse(int(h)) for h in hashed] == [int(x) for x in words]
+    assert len(set(hashed.tolist())) == len(set(words.tolist()))
+
+
 @pytest.mark.parametrize("rows, n", [(1, 128256), (3, 1000), (2, 33), (1, 1)])
 def test_argmax(rows, n):
     rng = np.random.default_rng(n)

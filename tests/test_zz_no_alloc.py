@@ -29,6 +29,10 @@ def _both(device, w, mode, width):
                            width=width, want_greedy=True)  # fmt: skip
     torch.cuda.synchronize()
     assert int(static.status.item()) & _lib.STATUS_INTERNAL == 0
+    # and both against the CPU oracle, not only against each other
+    want = helpers.oracle_run(w, mode)
+    helpers.compare(want, static, width, max_fragile=1)
+    helpers.compare(want, with_workspace, width, max_fragile=1)
     return with_workspace, static
 
 
@@ -68,3 +72,36 @@ def test_static_scratch_rejects_what_it_cannot_hold(device):
             sample_static(logits, options, uniform=torch.zeros(logits.shape[0], device=device))
     args = _lib.SampleArgs()
     assert _lib.lib.leat_sample_static(C.byref(args), None) == _lib.E_ARGUMENT
+
+
+def test_static_scratch_edges(device):
+    """What the header promises beside the main path: rows with top_k above 64 are settled by the
+    multi-pass routine (status bit FALLBACK) and still equal the oracle; 16-bit logits are refused;
+    a call with no rows clears the status word on request and launches nothing."""
+    import torch
+
+    from leat_b200 import _lib, workloads
+    from leat_b200.sampler import Sampler, sample_static
+    from tests import helpers
+
+    w = workloads.config2(rows=6, vocab=50048)
+    w.options[:, 1] = 100.0  # top_k beyond the 64 the fixed scratch selects in one pass
+    t = lambda x: None if x is None else torch.as_tensor(x).to(device)  # noqa: E731
+    got = sample_static(t(w.logits), t(w.options), None, t(w.position), history=t(w.history), penalties=t(w.penalties),
+                        uniform=t(w.uniform), width=128, want_greedy=True)  # fmt: skip
+    torch.cuda.synchronize()
+    assert int(got.status.item()) & _lib.STATUS_FALLBACK
+    want = helpers.oracle_run(w, "U", order="sequential")
+    firm = want.margin >= helpers.FRAGILE
+    np.testing.assert_array_equal(got.ids.cpu().numpy().ravel()[firm], want.ids.ravel()[firm])
+    np.testing.assert_array_equal(got.kept.cpu().numpy()[firm], want.kept[firm])
+    np.testing.assert_array_equal(got.cut.cpu().numpy()[firm], want.cut[firm])
+    with pytest.raises(ValueError):
+        sample_static(t(w.logits).to(torch.bfloat16), t(w.options), uniform=t(w.uniform))
+    args, keep = Sampler._args(None, torch.zeros((0, 1024), device=device), t(w.options[:1]), None, 0, None, None, None,
+                               None, None, 0)  # fmt: skip
+    status = torch.full((1,), 7, dtype=torch.int32, device=device)
+    args.status, args.out_ids = status.data_ptr(), status.data_ptr()
+    assert _lib.lib.leat_sample_static(C.byref(args), None) == _lib.OK
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
