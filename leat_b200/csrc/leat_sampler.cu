@@ -320,10 +320,12 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
       if (per > per_row) per = per_row;
       blocks = per * P.rows;
     }
-    // few rows, but more than a handful: their floors are worked out first, one block per row,
-    // instead of by each of the many blocks that share a row (measured: 16 rows 16.8 against 19.8
-    // us per step, 72 rows 24.3 against 29.6; a single row 13.5 against 12.1)
-    const int floors_first = (P.rows >= 4 && (per > 0 || items <= blocks)) ? 1 : 0;
+    // Unless the rows are about as many as the blocks (then a block works out little more than one
+    // floor anyway) or a mere handful, the floors are worked out first, one block per row, instead
+    // of by each of the blocks that share a row (measured, us per step: 16 rows 16.8 against 19.8,
+    // 72 rows 24.3 against 29.6, 256 rows 2 to 4 better, 512 rows 2 to 3 worse, a single row 13.5
+    // against 12.1)
+    const int floors_first = (P.rows >= 4 && P.rows * 4 < h->sm_count * 4 * 3) ? 1 : 0;
     // the first launch is a programmatic dependent of whatever comes before it in the stream (the
     // kernel that writes the logits): its blocks may be placed early, and wait before they read
     if (floors_first) {
