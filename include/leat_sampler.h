@@ -128,16 +128,13 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
                         int32_t max_vocab, int32_t k_max, leat_sampler_t** out);
 int leat_sampler_destroy(leat_sampler_t* handle);
 
-/* Launch shape override for experiments: threads per block (128, 256 or 512; 0 = automatic) and
+/* Launch shape override, for tests that run one input through several shapes: threads per block (128, 256 or 512; 0 = automatic) and
    blocks per row (0 = automatic). */
 int leat_sampler_tune(leat_sampler_t* handle, int32_t threads, int32_t slices);
 /* The filter path (floor per row, one streaming filter, finish from the row's list) is taken for
    16-byte aligned rows of at least 16384 tokens without a dense seen mask; 0 turns it off and every
-   row goes through the fused kernel. */
+   row goes through the fused kernel (for tests that run one input through both). */
 int leat_sampler_tune_filter(leat_sampler_t* handle, int32_t enabled);
-/* Stages of the shared-memory ring the stream's bulk copies fill: 0 = automatic, 2..8 = that many,
-   negative = no ring (the stream loads into registers instead). */
-int leat_sampler_tune_ring(leat_sampler_t* handle, int32_t stages);
 /* The launch shape the handle would use for (rows, vocab): writes threads, slices, blocks. */
 int leat_sampler_plan(const leat_sampler_t* handle, int32_t rows, int32_t vocab, int32_t history_cap,
                       int32_t* threads, int32_t* slices, int32_t* shared_bytes);

@@ -24,7 +24,7 @@ _ERRORS = {
 
 EXPORTS = [
     "leat_sampler_workspace_bytes", "leat_sampler_create", "leat_sampler_destroy",
-    "leat_sampler_tune", "leat_sampler_tune_filter", "leat_sampler_tune_ring", "leat_sampler_plan", "leat_sampler_last_launches",
+    "leat_sampler_tune", "leat_sampler_tune_filter", "leat_sampler_plan", "leat_sampler_last_launches",
     "leat_sampler_time_kernels", "leat_sampler_kernel_times",
     "leat_sampler_last_cuda_error", "leat_sample", "leat_argmax", "leat_cutoff",
     "leat_verify_draft", "leat_settle_draft", "leat_topk_local", "leat_sample_from_candidates", "leat_sample_static",
@@ -71,7 +71,6 @@ def _load() -> C.CDLL:
     lib.leat_sampler_create.argtypes = [p, sz, i32, i32, i32, i32, C.POINTER(p)]
     lib.leat_sampler_destroy.argtypes = [p]
     lib.leat_sampler_tune.argtypes = [p, i32, i32]
-    lib.leat_sampler_tune_ring.argtypes = [p, i32]
     lib.leat_sampler_tune_filter.argtypes = [p, i32]
     lib.leat_sampler_plan.argtypes = [p, i32, i32, i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32)]
     lib.leat_sampler_last_launches.argtypes = [p]

@@ -65,7 +65,7 @@ int cap_for(int keep) { return keep <= 512 ? 2048 : 4096; }
 
 struct leat_sampler {
   int device, max_rows, max_vocab, k_max, keep, cap;
-  int tune_threads, tune_slices, tune_stages, tune_no_ring, tune_no_filter, has_list;
+  int tune_threads, tune_slices, tune_no_filter, has_list;
   // optional per-kernel timing of a call: the kernels stamp their begin and end in the workspace
   int timing;
   // a launch failed after lists were written: the next call empties the lists first
@@ -129,11 +129,10 @@ Plan make_plan(const leat_sampler* h, int rows, int vocab, int history_cap, bool
   p.ht_size = has_history ? next_pow2(history_cap * 2 < 64 ? 64 : history_cap * 2) : 0;
   // the ring of bulk copies: as many stages as fit a block's share of shared memory
   p.ring_stages = 0;
-  if (vec == 4 && !h->tune_no_ring) {
+  if (vec == 4) {
     const size_t stage = (size_t)p.threads * RING_PER_THREAD * 4;
     const size_t used = fixed_shared(h->cap, h->keep) + ((size_t)p.ht_size * 4 + 127) / 128 * 128;
     int stages = used < kSharedPerBlockTarget ? (int)((kSharedPerBlockTarget - used) / stage) : 0;
-    if (h->tune_stages) stages = h->tune_stages;
     if (stages > MAX_RING_STAGES) stages = MAX_RING_STAGES;
     if (stages >= 2) p.ring_stages = stages;
   }
@@ -404,7 +403,7 @@ int leat_sampler_create(void* workspace, size_t bytes, int32_t device, int32_t m
   if (!h) return LEAT_E_ARGUMENT;
   h->device = device; h->max_rows = max_rows; h->max_vocab = max_vocab; h->k_max = k_max;
   h->keep = keep_for(k_max); h->cap = cap_for(h->keep);
-  h->tune_threads = 0; h->tune_slices = 0; h->tune_stages = 0; h->tune_no_ring = 0; h->tune_no_filter = 0; h->has_list = 1; h->timing = 0; h->dirty = 0; h->launches = 0;
+  h->tune_threads = 0; h->tune_slices = 0; h->tune_no_filter = 0; h->has_list = 1; h->timing = 0; h->dirty = 0; h->launches = 0;
   h->L = layout_for(max_rows, max_vocab, h->keep);
   h->ws = static_cast<unsigned char*>(workspace);
   if (bytes < h->L.total || !aligned(workspace, 256)) { delete h; return LEAT_E_WORKSPACE; }
@@ -446,13 +445,6 @@ int leat_sampler_tune(leat_sampler_t* h, int32_t threads, int32_t slices) {
 int leat_sampler_tune_filter(leat_sampler_t* h, int32_t enabled) {
   if (!h) return LEAT_E_ARGUMENT;
   h->tune_no_filter = enabled ? 0 : 1;
-  return LEAT_OK;
-}
-
-int leat_sampler_tune_ring(leat_sampler_t* h, int32_t stages) {
-  if (!h || stages > MAX_RING_STAGES) return LEAT_E_ARGUMENT;
-  h->tune_no_ring = stages < 0 ? 1 : 0;
-  h->tune_stages = stages > 0 ? stages : 0;
   return LEAT_OK;
 }
 
@@ -690,7 +682,7 @@ int static_setup(int device, StaticDevice** out) {
     leat_sampler& h = sd.handle;
     h.device = device; h.max_rows = kStaticRows; h.max_vocab = kStaticVocab; h.k_max = kStaticK;
     h.keep = keep_for(kStaticK); h.cap = cap_for(h.keep);
-    h.tune_threads = 0; h.tune_slices = 0; h.tune_stages = 0; h.tune_no_ring = 0; h.tune_no_filter = 0; h.has_list = 0; h.timing = 0; h.dirty = 0; h.launches = 0;
+    h.tune_threads = 0; h.tune_slices = 0; h.tune_no_filter = 0; h.has_list = 0; h.timing = 0; h.dirty = 0; h.launches = 0;
     Layout& L = h.L;
     L.cells = kStaticCells;
     size_t at = 0;

@@ -129,9 +129,6 @@ class Sampler:
     def tune_filter(self, enabled: bool = True) -> None:
         _lib.check(_lib.lib.leat_sampler_tune_filter(self.handle, int(enabled)), "leat_sampler_tune_filter")
 
-    def tune_ring(self, stages: int = 0) -> None:
-        _lib.check(_lib.lib.leat_sampler_tune_ring(self.handle, stages), "leat_sampler_tune_ring")
-
     def plan(self, rows: int, vocab: int, history_cap: int = 0) -> tuple[int, int, int]:
         t, s, b = C.c_int32(), C.c_int32(), C.c_int32()
         _lib.check(_lib.lib.leat_sampler_plan(self.handle, rows, vocab, history_cap, C.byref(t),
