@@ -46,6 +46,16 @@ L2_BYTES = 126 << 20
 TRAFFIC_PER_ALGORITHMIC_BYTE = 1.02
 HEADLINE = 5  # the configuration every N runs
 CPU_SAMPLE_ROWS = 32  # rows of the headline workload the CPU arm times per step
+# Steps a replayed graph holds, back to back.  In leat's engine the sampler's kernels sit inside the
+# decode step's graph, after the model's; launching a graph (about 4.5 us here) is the engine's cost,
+# paid once per decode step whatever the sampler does, so a graph of one sampler step would count it
+# against the sampler.  (The line also carries the figure for one step per graph.)
+STEPS_PER_GRAPH = 10
+
+
+def steps_per_graph(steps: int) -> int:
+    """The largest of 10, 5, 4, 2, 1 that divides the number of timed steps."""
+    return next(s for s in (10, 5, 4, 2, 1) if steps % s == 0)
 
 WORKLOAD_NAMES = {1: "c1_single_row", 2: "c2_server_step", 3: "c3_large_batch", 4: "c4_draft_verify", 5: "c5_vocab_sharded"}
 SHAPES_ROWS = {1: 1, 2: 16, 3: 256, 4: 72, 5: 512}
@@ -256,13 +266,14 @@ def time_config(step, pool_len: int, warmup: int, min_steps: int = 200) -> dict:
     for i in range(max(warmup, 3)):
         step(i)
     torch.cuda.synchronize()
-    graph = capture(step, pool_len)
-    replays = max(8, -(-min_steps // pool_len))
+    inner = pool_len if pool_len >= STEPS_PER_GRAPH else STEPS_PER_GRAPH * pool_len  # (whole passes over the pool)
+    graph = capture(step, inner)
+    replays = max(8, -(-min_steps // inner))
     graph.replay()
     total, each = timed_replays(lambda i: graph.replay(), replays)
-    per_step = np.array(each) / pool_len
-    return {"mean_ms": total / (replays * pool_len), "median_ms": float(np.median(per_step)),
-            "p95_ms": float(np.percentile(per_step, 95)), "replays": replays, "steps_per_replay": pool_len}  # fmt: skip
+    per_step = np.array(each) / inner
+    return {"mean_ms": total / (replays * inner), "median_ms": float(np.median(per_step)),
+            "p95_ms": float(np.percentile(per_step, 95)), "replays": replays, "steps_per_replay": inner}  # fmt: skip
 
 
 def kernel_timeline(sampler, dw, replays: int = 7) -> dict:
@@ -376,13 +387,17 @@ def run_single(args) -> None:
 
     # the headline: exactly K steps of the largest configuration, one graph replay and one event each
     w, dw, kernels, launches_per_step = headline
-    graphs = [capture(lambda i, j=j: dw.step(sampler, j), 1) for j in range(len(dw.pool))]
-    for i in range(args.warmup):
-        graphs[i % len(graphs)].replay()
+    per_graph = steps_per_graph(args.steps)
+    graph = capture(lambda i: dw.step(sampler, i), per_graph)
+    single = capture(lambda i: dw.step(sampler, i), 1)
+    for i in range(-(-args.warmup // per_graph)):
+        graph.replay()
     with ClockSampler(device.index) as clocks:
-        total, each = timed_replays(lambda i: graphs[i % len(graphs)].replay(), args.steps)
+        total, each = timed_replays(lambda i: graph.replay(), args.steps // per_graph)
         ms = total / args.steps
-        keep_busy(lambda i: graphs[i % len(graphs)].replay(), ms)
+        each = [x / per_graph for x in each]
+        keep_busy(lambda i: graph.replay(), ms * per_graph)
+        single_total, _ = timed_replays(lambda i: single.replay(), args.steps)
         # end to end through the public call: host logits in pinned memory, copied in every step;
         # ids read back every step
         host_logits = torch.as_tensor(w.logits).pin_memory()
@@ -418,9 +433,12 @@ def run_single(args) -> None:
         "warmup": args.warmup, "ms_per_step": ms, "median_ms": float(np.median(each)), "p95_ms": float(np.percentile(each, 95)),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": headline_config(1, w.vocab),
+        "steps_per_graph": per_graph, "ms_per_step_one_step_per_graph": single_total / args.steps,
         "notes": {"l2": dw.l2_note,
-                  "timing": "CUDA events on the launching stream: one before the K steps, one after each; every step is "
-                            "a replay of a CUDA graph holding one leat_sample call; ms_per_step = region / K"},
+                  "timing": "CUDA events on the launching stream: one before the K steps, one after each replay of a CUDA graph "
+                            f"holding {per_graph} consecutive leat_sample calls (a decode graph holds the model's kernels around "
+                            "the sampler's; the graph's own launch is the engine's cost); ms_per_step = region / K, median and "
+                            "p95 over the replays, per step"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE * w.logit_bytes, "peak_kind": peak_kind,
                      "kernel": "the whole call: filter_kernel, finish_list_kernel, sample_kernel",
@@ -476,18 +494,20 @@ def run_sharded(args) -> None:
     for i in range(args.warmup):
         step(i)
     torch.cuda.synchronize()
-    replay, how = sharded.replayable(pool, options, seed, position, history, penalties, uniform, out)
+    per_graph = steps_per_graph(args.steps)
+    replay, how = sharded.replayable(pool, options, seed, position, history, penalties, uniform, out, per_graph)
     for i in range(3):
         replay(i)
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
     with ClockSampler(local) as clocks:
-        total, each = timed_replays(replay, args.steps)
+        total, each = timed_replays(replay, args.steps // per_graph)
+        each = [x / per_graph for x in each]
         stats = torch.tensor([total / args.steps, float(np.median(each)), float(np.percentile(each, 95))], device=device)
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
         ms, median_ms, p95_ms = (float(x) for x in stats.tolist())
-        keep_busy(replay, ms)
+        keep_busy(replay, ms * per_graph)
     dist.barrier()
     torch.cuda.synchronize()
     replayed_ids = out.clone()  # what the last of the replayed steps left (checked below)
@@ -543,7 +563,7 @@ def run_sharded(args) -> None:
             "metric": "sampler rows/s", "value": w.rows / (ms * 1e-3), "unit": "rows/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "median_ms": median_ms, "p95_ms": p95_ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": headline_config(world, w.vocab),
+            "config": headline_config(world, w.vocab), "steps_per_graph": per_graph,
             "notes": {"l2": f"logits pool of {len(pool)} buffers per rank cycled, larger than L2" if len(pool) > 1
                       else "each rank's slice is larger than L2",
                       "exchange": sharded.exchange_note,

@@ -258,24 +258,23 @@ class ShardedSampler:
         results (peer); filter, candidates, second pass, finish (collective)."""
         return 5 if self.exchange_kind == "peer" else 4
 
-    def replayable(self, pool, options, seed, position, history, penalties, uniform, out):
-        """A function replay(i) that runs step i over pool[i % len(pool)] from captured CUDA graphs, as
-        a serving engine that replays captured decode steps would, and a sentence saying how.  With the
-        peer exchange a whole step is one graph; with the collective one, the two device steps are
-        graphs and the all-gather is issued between them."""
+    def replayable(self, pool, options, seed, position, history, penalties, uniform, out, per_graph: int = 1):
+        """A function replay(i) that runs `per_graph` consecutive steps (over pool[0], pool[1], ...
+        in turn) from captured CUDA graphs, as a serving engine that replays captured decode steps
+        would, and a sentence saying how.  With the peer exchange the steps are one graph; with the
+        collective one, each step's two device steps are graphs and the all-gather is issued between
+        them."""
         rows = pool[0].shape[0]
         side = torch.cuda.Stream()
         if self.exchange_kind == "peer":
-            graphs = []
+            graph = torch.cuda.CUDAGraph()
             with torch.cuda.stream(side):
-                for buffer in pool:
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g, stream=side):
-                        self.sample(buffer, options, seed, position, history=history, penalties=penalties,
+                with torch.cuda.graph(graph, stream=side):
+                    for j in range(per_graph):
+                        self.sample(pool[j % len(pool)], options, seed, position, history=history, penalties=penalties,
                                     uniform=uniform, out=out)  # fmt: skip
-                    graphs.append(g)
             torch.cuda.synchronize()
-            return (lambda i: graphs[i % len(graphs)].replay()), "every step is one replay of a CUDA graph holding the whole step"
+            return (lambda i: graph.replay()), f"every replay is one CUDA graph holding {per_graph} whole steps"
         selects, finish = [], torch.cuda.CUDAGraph()
         with torch.cuda.stream(side):
             for buffer in pool:
@@ -288,8 +287,9 @@ class ShardedSampler:
         torch.cuda.synchronize()
 
         def replay(i):
-            selects[i % len(selects)].replay()
-            self.exchange(rows)
-            finish.replay()
+            for j in range(per_graph):
+                selects[j % len(selects)].replay()
+                self.exchange(rows)
+                finish.replay()
 
         return replay, "the two device steps replayed from CUDA graphs, the all-gather issued eagerly between them"
