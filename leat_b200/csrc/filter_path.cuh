@@ -482,7 +482,9 @@ __global__ void __launch_bounds__(FILTER_THREADS, 4) filter_kernel(const __grid_
       st.row = b;
       if (!asked) ask_ahead(row, base);
       asked = false;
-      floor_l = block_floor<T>(P, b, runs, sorted, &rc, &known);
+      // (a handful of rows with one item per block: every block starts on its row at the same time,
+      // so no block would find the row's word there yet: no use looking)
+      floor_l = block_floor<T>(P, b, runs, sorted, &rc, &known, floors_first || items > (int)gridDim.x);
       async_wait_all();  // (each thread reads back what it asked for itself)
       if (!(floor_l < pos_inf())) continue;  // the row does not use the list
 #pragma unroll

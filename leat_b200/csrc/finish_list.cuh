@@ -183,6 +183,28 @@ __device__ __forceinline__ void fl_select(const unsigned long long* keys, int n,
   __syncthreads();
 }
 
+// How many keys of runs r0 .. r0 + W - 1 (descending runs of 32; runs at or past `nruns` and run
+// `mine` do not count) lie above `key`: W binary searches side by side.
+template <int W>
+__device__ __forceinline__ int fl_above(const unsigned long long* runs, unsigned long long key, int r0, int nruns, int mine) {
+  int pos[W];
+#pragma unroll
+  for (int r = 0; r < W; ++r) pos[r] = 0;
+#pragma unroll
+  for (int step = 16; step > 0; step >>= 1) {
+#pragma unroll
+    for (int r = 0; r < W; ++r)
+      if (runs[((r0 + r) & (FL_SORT / 32 - 1)) * 32 + pos[r] + step - 1] > key) pos[r] += step;
+  }
+  int total = 0;
+#pragma unroll
+  for (int r = 0; r < W; ++r) {
+    if (pos[r] == 31 && runs[((r0 + r) & (FL_SORT / 32 - 1)) * 32 + 31] > key) pos[r] = 32;
+    if (r0 + r < nruns && r0 + r != mine) total += pos[r];
+  }
+  return total;
+}
+
 // Sorts the non-zero keys of src[0..c), c <= FL_SORT, all distinct, likeliest first into dst; `runs`
 // is FL_SORT words of scratch.  Runs of 32 are sorted in registers; a key's place is its place in
 // its run plus, for every other run, the number of keys there above it (eight searches at a time).
@@ -216,23 +238,16 @@ __device__ __forceinline__ void fl_sort(const unsigned long long* src, int c, un
   int place[PER];
 #pragma unroll
   for (int q = 0; q < PER; ++q) place[q] = lane;
+  if (nruns <= 4) {  // (a top_k of 64 leaves three runs: no need to search eight)
+#pragma unroll
+    for (int q = 0; q < PER; ++q)
+      if (key[q] != 0ull) place[q] += fl_above<4>(runs, key[q], 0, nruns, q * WARPS + warp);
+  } else {
 #pragma unroll 1
-  for (int r0 = 0; r0 < nruns; r0 += 8) {
+    for (int r0 = 0; r0 < nruns; r0 += 8) {
 #pragma unroll
-    for (int q = 0; q < PER; ++q) {
-      if (key[q] == 0ull) continue;
-      int pos[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-      for (int step = 16; step > 0; step >>= 1) {
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-          if (runs[((r0 + r) & (FL_SORT / 32 - 1)) * 32 + pos[r] + step - 1] > key[q]) pos[r] += step;
-      }
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        if (pos[r] == 31 && runs[((r0 + r) & (FL_SORT / 32 - 1)) * 32 + 31] > key[q]) pos[r] = 32;
-        if (r0 + r < nruns && r0 + r != q * WARPS + warp) place[q] += pos[r];
-      }
+      for (int q = 0; q < PER; ++q)
+        if (key[q] != 0ull) place[q] += fl_above<8>(runs, key[q], r0, nruns, q * WARPS + warp);
     }
   }
 #pragma unroll
