@@ -59,8 +59,9 @@ enum {
 /* Arguments of leat_sample; stands in for the arguments of sample() at leat/sampler.py:31-34. */
 typedef struct leat_sample_args {
   /* logits (rows, vocab), row b at element b * row_stride: float32, or bfloat16 / float16 with
-     LEAT_FLAG_LOGITS_BF16 / LEAT_FLAG_LOGITS_F16 (then 16-byte aligned rows of a multiple of 8
-     tokens, at least 16384, no dense seen mask: LEAT_E_ARGUMENT otherwise) */
+     LEAT_FLAG_LOGITS_BF16 / LEAT_FLAG_LOGITS_F16 (any shape float32 logits may have; 16-byte
+     aligned rows of a multiple of 8 tokens, at least 16384 of them, without a dense seen mask are
+     the fast case, everything else is streamed with two-byte loads) */
   const void* logits;
   int32_t rows;
   int32_t vocab;

@@ -277,8 +277,6 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
                                      P.history ? next_pow2(P.history_cap * 2 < 64 ? 64 : P.history_cap * 2) : 0, &ht, &words);
     if (bytes == 0 || bytes > (size_t)kMostShared) filtered = false;
   }
-  // 16-bit logits are read by the filter path only (and, row by row, by the multi-pass routine)
-  if (P.dtype != 0 && (!filtered || P.cand_count)) return LEAT_E_ARGUMENT;
   // LEAT_FLAG_CLEAR_STATUS: filter_kernel clears the word on the filter path, a memset node otherwise
   if ((P.flags & LEAT_FLAG_CLEAR_STATUS) && P.status && !filtered &&
       cuda_failed(cudaMemsetAsync(P.status, 0, sizeof(int), stream), "cudaMemsetAsync")) return LEAT_E_CUDA;
@@ -286,7 +284,9 @@ int launch_sample(leat_sampler* h, KParams& P, cudaStream_t stream) {
     P.stamps = reinterpret_cast<unsigned long long*>(h->ws + h->L.stamps);
     if (cuda_failed(cudaMemsetAsync(P.stamps, 0, 16 * 8, stream), "cudaMemsetAsync")) return LEAT_E_CUDA;
   }
-  Plan plan = make_plan(h, P.rows, P.vocab, P.history_cap, P.history != nullptr, vec);
+  // (the ring of bulk copies moves float32 logits only: 16-bit rows without a list are streamed
+  // with plain loads)
+  Plan plan = make_plan(h, P.rows, P.vocab, P.history_cap, P.history != nullptr, P.dtype == 0 ? vec : 1);
   P.slices = plan.slices; P.slice_len = plan.slice_len; P.bm_words = plan.bm_words; P.ht_size = plan.ht_size;
   P.ring_stages = plan.ring_stages;  // 0 unless rows are 16-byte aligned multiples of four floats
   if (plan.shared > kMostShared) return LEAT_E_CAPACITY;  // (a history this long with top_k this large)

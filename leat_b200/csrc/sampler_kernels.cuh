@@ -781,6 +781,14 @@ struct Tracked {
 
 #include "filter_path.cuh"
 
+// Logit i of the row that begins at `row` (the row's first byte, dressed as a float pointer),
+// whatever the logits' format.
+__device__ __forceinline__ float row_logit(const KParams& P, const float* __restrict__ row, int i) {
+  if (P.dtype == 0) return row[i];
+  const unsigned short h = reinterpret_cast<const unsigned short*>(row)[i];
+  return P.dtype == 1 ? __uint_as_float((uint32_t)h << 16) : __half2float(__ushort_as_half(h));
+}
+
 // The first `cap` scores of a top-k / min-p slice go straight into the candidate buffer (exact,
 // penalties applied); one rebuild gives the first threshold.  Returns where the stream starts.
 template <bool PEN>
@@ -797,7 +805,7 @@ __device__ __noinline__ int slice_fill(const KParams& P, const RowCfg& rc, const
 #pragma unroll
     for (int j = 0; j < FB; ++j) {
       const int i = base + j * nt + tid;
-      raw[j] = i < fill_end ? row[i] : 0.0f;
+      raw[j] = i < fill_end ? row_logit(P, row, i) : 0.0f;
     }
 #pragma unroll 1
     for (int j = 0; j < FB; ++j) {
@@ -931,7 +939,7 @@ __device__ __noinline__ void stream_plain(const KParams& P, const RowCfg& rc, co
           bool in_history = false;
           if (PEN && P.history) in_history = leat::in_history(h.keys, h.mask, idx);
           if (!in_history) {
-            l = row[idx];
+            l = row_logit(P, row, idx);
             if (PEN && seen_row && seen_row[idx]) l = penalised(l, 1, rc);
             if (rounds == 0) {
               if ((mode == M_ARGMAX_L || rc.track) && (l > t.gl || (l == t.gl && idx < t.gid))) { t.gl = l; t.gid = idx; }
@@ -1035,7 +1043,8 @@ __device__ __forceinline__ void sample_block(const KParams& P, const int b, cons
   int S = P.slices;
   const int begin = slice * P.slice_len;
   int end = min(P.vocab, begin + P.slice_len);
-  const float* row = P.logits + (size_t)b * P.row_stride;
+  const float* row = P.dtype == 0 ? P.logits + (size_t)b * P.row_stride
+                                  : reinterpret_cast<const float*>(reinterpret_cast<const unsigned short*>(P.logits) + (size_t)b * P.row_stride);
   const uint8_t* seen_row = (PEN && P.seen) ? P.seen + (size_t)b * P.seen_stride : nullptr;
   // the row's options and the buffer's description live in shared memory, not in registers
   // loads nothing else depends on go out first: the first history ids, the list's length and entry
@@ -1072,8 +1081,6 @@ __device__ __forceinline__ void sample_block(const KParams& P, const int b, cons
     sm.share_greedy = 0u; sm.share_gumbel = 0u; sm.share_min = 0xFFFFFFFFu;
     h.raw = hraw; h.keys = hkeys; h.counts = hcnt; h.mask = P.ht_size - 1; h.begin = begin;
     sm.floor_l = P.list ? __uint_as_float(floor_bits) : __uint_as_float(0x7F800000u);
-    // the streaming code reads float32 only: a 16-bit row without a list is left to the multi-pass routine
-    if (P.dtype != 0 && !(sm.floor_l < __uint_as_float(0x7F800000u))) { rc.mode = M_GENERAL; c.mode = M_GENERAL; }
     // a soft cap is applied where candidates are few: here, by the multi-pass routine
     if (P.softcap > 0.0f) { rc.mode = M_GENERAL; c.mode = M_GENERAL; }
     sm.s_floor = neg_inf();

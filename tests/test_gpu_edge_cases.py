@@ -237,12 +237,3 @@ def test_sixteen_bit_logits(sampler, device, dtype, mode):
             assert want.margin[b] < 1e-4, (b, ids[b], want.ids[b, 0], kept[b], want.kept[b], cut[b], want.cut[b])
             soft += 1
     assert soft <= 1
-
-
-def test_sixteen_bit_logits_need_the_filter_path(sampler, device):
-    import torch
-
-    logits = torch.zeros((2, 1000), dtype=torch.bfloat16, device=device)  # too narrow for a list
-    with pytest.raises(ValueError):
-        sampler.sample_full(logits, torch.as_tensor(_options(2)).to(device), torch.zeros(2, dtype=torch.int32).to(device).to(torch.uint32),
-                            torch.zeros(2, dtype=torch.int32, device=device))  # fmt: skip

@@ -42,9 +42,10 @@ class PeerShardsOnOneGpu:
         for shard in self.shards:
             _lib.lib.leat_shard_destroy(shard)
 
-    def step(self, w, mode, leave_out=None):
+    def step(self, w, mode, leave_out=None, dtype=None):
         """One step of every rank; returns each rank's Sampled.  `leave_out`: a rank that does not
-        take the step at all (the others must notice, not hang)."""
+        take the step at all (the others must notice, not hang); `dtype`: the slices' format on the
+        device, if not float32."""
         import torch
 
         from leat_b200 import _lib
@@ -60,6 +61,7 @@ class PeerShardsOnOneGpu:
         for r in ranks:
             start, stop = self.bounds[r]
             part = torch.as_tensor(np.ascontiguousarray(w.logits[:, start:stop])).to(d)
+            part = part if dtype is None else part.to(dtype)
             a, keep = self.samplers[r]._args(part, options, seed, position, None, history, None, penalties, uniform,
                                              0, start, self.vocab)  # fmt: skip
             out = Sampled(torch.empty((self.rows, 1), dtype=torch.int32, device=d),

@@ -12,7 +12,7 @@ from tests import helpers
 pytestmark = pytest.mark.gpu
 
 
-def _sharded_on_one_gpu(device, w, parts, mode, cap=128, k_max=64, width=64):
+def _sharded_on_one_gpu(device, w, parts, mode, cap=128, k_max=64, width=64, dtype=None):
     import torch
 
     from leat_b200 import _lib, workloads
@@ -31,6 +31,7 @@ def _sharded_on_one_gpu(device, w, parts, mode, cap=128, k_max=64, width=64):
     for r in range(parts):
         start, stop = workloads.shard_bounds(vocab, parts, r)
         part = torch.as_tensor(np.ascontiguousarray(w.logits[:, start:stop])).to(device)
+        part = part if dtype is None else part.to(dtype)  # (the slices' format on the device)
         a, keep = sampler._args(part, options, seed, position, None, history, None, penalties,
                                 uniform if mode == "U" else None, 0, start, vocab)  # fmt: skip
         _lib.check(_lib.lib.leat_topk_local(sampler.handle, C.byref(a), value[r].data_ptr(), ids[r].data_ptr(),
