@@ -715,6 +715,7 @@ int static_setup(int device, StaticDevice** out) {
 int leat_sample_static(const leat_sample_args* a, leat_stream_t stream) {
   if (!a || !a->out_ids) return LEAT_E_ARGUMENT;
   if (a->rows > kStaticRows || a->vocab > kStaticVocab) return LEAT_E_CAPACITY;
+  if (a->flags & (LEAT_FLAG_LOGITS_BF16 | LEAT_FLAG_LOGITS_F16)) return LEAT_E_ARGUMENT;  // float32 logits only
   if (a->rows == 0) {  // nothing to sample; the status word is still cleared on request, as leat_sample does
     if (a->vocab <= 0) return LEAT_E_ARGUMENT;
     if ((a->flags & LEAT_FLAG_CLEAR_STATUS) && a->status &&
