@@ -39,11 +39,10 @@ sys.path.insert(0, str(ROOT))
 FALLBACK_HBM_GBS = 6650.0  # an earlier measurement on this pool, used when MEASURED_PEAKS.json is absent
 NORTH_STAR_HBM_GBS = 8000.0
 L2_BYTES = 126 << 20
-# DRAM bytes filter_kernel moves per algorithmic byte, from one ncu capture of three launches on 160
-# rows of the large-batch configuration: (dram__bytes_read.sum + dram__bytes_write.sum) / (B x V x 4)
-# = (167.80 + 3.90) MB / 167.77 MB.  Traffic grows with the rows and the vocabulary, so it is
-# scaled to the launch being reported.
-TRAFFIC_PER_ALGORITHMIC_BYTE = 1.02
+# DRAM bytes filter_kernel moves per algorithmic byte, from one ncu capture of a launch on this very
+# workload (512 rows x 201088): (dram__bytes_read.sum + dram__bytes_write.sum) / (B x V x 4)
+# = (411.93 + 3.77) MB / 411.83 MB; 160 rows of the large-batch configuration gave 1.02.
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0094
 HEADLINE = 5  # the configuration every N runs
 CPU_SAMPLE_ROWS = 32  # rows of the headline workload the CPU arm times per step
 # Steps a replayed graph holds, back to back.  In leat's engine the sampler's kernels sit inside the
