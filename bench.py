@@ -378,6 +378,13 @@ def run_single(args) -> None:
             "filter_kernel_gbs": None if filter_gbs is None else round(filter_gbs, 1),
             "filter_kernel_frac_of_measured": None if filter_gbs is None else round(filter_gbs / peak, 4),
         }  # fmt: skip
+        if dtype is None:
+            # ops.argmax over the same logits (what leat's drafters run, leat/draft.py:166): one launch
+            arg = time_config(lambda i, dw=dw: sampler.argmax(dw.pool[i % len(dw.pool)]), len(dw.pool), args.warmup)
+            arg_gbs = dw.logit_bytes / (arg["median_ms"] * 1e-3) / 1e9
+            all_configs[WORKLOAD_NAMES[number]]["argmax"] = {
+                "us_per_call": round(arg["median_ms"] * 1e3, 2), "p95_us": round(arg["p95_ms"] * 1e3, 2),
+                "hbm_gbs": round(arg_gbs, 1), "frac_of_measured": round(arg_gbs / peak, 4)}  # fmt: skip
         if number == HEADLINE:
             headline = (w, dw, kernels, launches_per_step)  # stays resident for the timed region below
         else:

@@ -175,7 +175,9 @@ int leat_sample(leat_sampler_t* handle, const leat_sample_args* args, leat_strea
 int leat_sample_static(const leat_sample_args* args, leat_stream_t stream);
 
 /* ops.argmax(): leat/ops.py:496-500 and leat/kernels/argmax.py:48-61.  x (rows, vocab) float32 ->
-   out (rows,) int32, the first index of each row's largest value. */
+   out (rows,) int32, the first index of each row's largest value (a NaN is never the largest; a row
+   of nothing but -inf and NaN answers 0).  One launch that streams x once for 16-byte aligned rows of
+   a multiple of four values, at least 4096 of them; the sampler's greedy path otherwise. */
 int leat_argmax(leat_sampler_t* handle, const float* x, int32_t rows, int32_t vocab,
                 int64_t row_stride, int32_t* out, int32_t* status, leat_stream_t stream);
 

@@ -20,6 +20,7 @@ constexpr int kMaxSliceLen = 1 << 20;  // a block may take a whole row
 constexpr int kSliceAlign = 128;
 constexpr int kMaxK = 1024;
 constexpr int kSpareCells = 4096;
+constexpr int kArgmaxMinVocab = 4096;  // shorter rows go through the sampler's own greedy path
 constexpr int kListCap = 4096;        // (logit, index) pairs a row's filter may list
 constexpr int kFilterMinVocab = 16384;  // narrower rows are not worth three launches
 
@@ -511,6 +512,29 @@ int leat_argmax(leat_sampler_t* h, const float* x, int32_t rows, int32_t vocab, 
   if (rc != LEAT_OK) return rc;
   if (!out) return LEAT_E_ARGUMENT;
   P.force_greedy = 1;
+  if (pick_vec(P) == 4 && vocab >= kArgmaxMinVocab && !h->tune_no_filter) {
+    // rows of whole aligned vectors: one launch of a kernel of its own
+    h->launches = 0;
+    if (rows == 0) return LEAT_OK;
+    int dev = -1;
+    if (cuda_failed(cudaGetDevice(&dev), "cudaGetDevice")) return LEAT_E_CUDA;
+    if (dev != h->device) return LEAT_E_DEVICE;
+    // enough blocks to fill the GPU, none with less than one round of loads to do
+    int slices = (h->sm_count * 4 + rows - 1) / rows;
+    const int rounds = (vocab + AM_ROUND - 1) / AM_ROUND;
+    if (slices > rounds) slices = rounds;
+    if (slices > AM_MAX_SLICES) slices = AM_MAX_SLICES;
+    if (slices < 1) slices = 1;
+    const int span = round_up((vocab + slices - 1) / slices, 1024);
+    slices = (vocab + span - 1) / span;
+    const cudaError_t e = launch_dependent(argmax_kernel, dim3(slices, rows), dim3(AM_THREADS), 0, static_cast<cudaStream_t>(stream),
+                                           x, (int)vocab, (long long)row_stride, slices, span,
+                                           reinterpret_cast<unsigned long long*>(h->ws + h->L.keys),
+                                           reinterpret_cast<unsigned*>(h->ws + h->L.ticket), (int*)out);
+    if (cuda_failed(e, "argmax_kernel launch")) return LEAT_E_CUDA;
+    h->launches = 1;
+    return LEAT_OK;
+  }
   return launch_sample(h, P, static_cast<cudaStream_t>(stream));
 }
 

@@ -781,6 +781,8 @@ struct Tracked {
 
 #include "filter_path.cuh"
 
+#include "argmax_kernel.cuh"
+
 // Logit i of the row that begins at `row` (the row's first byte, dressed as a float pointer),
 // whatever the logits' format.
 __device__ __forceinline__ float row_logit(const KParams& P, const float* __restrict__ row, int i) {

@@ -108,14 +108,20 @@ def test_draws_equal_the_oracle(api):
         assert (want.margin[differ] < 1e-5).all() and len(differ) <= 2
 
 
-@pytest.mark.parametrize("rows, n", [(1, 128256), (3, 1000), (2, 33), (1, 1)])
+@pytest.mark.parametrize("rows, n", [(1, 128256), (3, 1000), (2, 33), (1, 1), (5, 151936), (300, 16384), (4, 262144),
+                                     (700, 4096), (2, 4100)])  # fmt: skip
 def test_argmax(api, device, rows, n):
+    """Rows of whole aligned vectors take the one-launch kernel, the others the sampler's greedy path."""
     import torch
 
     _, _, ops = api
     rng = np.random.default_rng(n)
     x = rng.integers(-50, 50, (rows, n)).astype(np.float32)  # many ties: the first one must win
     x[:, ::7] = -np.inf
+    x[-1, :] = -np.inf  # a row of nothing but -inf answers 0
+    if rows > 1:
+        x[0, : n // 2] = -np.inf  # the maximum lies in a later span
+        x[0, n - 1] = 60.0  # ... at the row's very end
     got = ops.argmax(torch.tensor(x, device=device))
     assert got.dtype == torch.int32
     np.testing.assert_array_equal(got.cpu().numpy(), x.argmax(-1, keepdims=True))
