@@ -5,6 +5,7 @@
 
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -519,9 +520,12 @@ int leat_argmax(leat_sampler_t* h, const float* x, int32_t rows, int32_t vocab, 
     int dev = -1;
     if (cuda_failed(cudaGetDevice(&dev), "cudaGetDevice")) return LEAT_E_CUDA;
     if (dev != h->device) return LEAT_E_DEVICE;
-    // enough blocks to fill the GPU, none with less than one round of loads to do
+    // enough blocks to fill the GPU, none with less than one round of loads to do, and with many
+    // rows two rounds a block: short blocks, handed out as SMs fall free, leave no tail (measured,
+    // 256 x 262144: 40.5 us against 45.7 with a third of a row per block)
     int slices = (h->sm_count * 4 + rows - 1) / rows;
     const int rounds = (vocab + AM_ROUND - 1) / AM_ROUND;
+    if (slices < (rounds + 1) / 2) slices = (rounds + 1) / 2;
     if (slices > rounds) slices = rounds;
     if (slices > AM_MAX_SLICES) slices = AM_MAX_SLICES;
     if (slices < 1) slices = 1;
