@@ -231,9 +231,10 @@ __device__ __forceinline__ float chunk_maximum_side_by_side(const void* row, int
   return mine;
 }
 
-template <typename T>
+// `meanwhile` runs once the sample's loads have been waited for, before the first barrier.
+template <typename T, typename F>
 __device__ __forceinline__ void sample_maxima(const void* row, int V, int vecs, unsigned long long* runs, float* sorted,
-                                              bool many_rows) {
+                                              bool many_rows, F meanwhile) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   unsigned long long key = 0ull;
   if (tid < SAMPLE_CHUNKS) {
@@ -255,6 +256,7 @@ __device__ __forceinline__ void sample_maxima(const void* row, int V, int vecs, 
     }
     runs[tid] = key;
   }
+  meanwhile();
   __syncthreads();
   if (tid < SAMPLE_CHUNKS) {
     // ... and a maximum's place is its place in its run plus the maxima above it in the other runs
@@ -318,14 +320,17 @@ __device__ __forceinline__ float block_floor(const KParams& P, int b, unsigned l
     const unsigned long long have = *known;
     if (have & INFO_READY) return info_floor(have);
   }
-  if (tid < 32) {
-    uint32_t unused;
-    const RowIn in = row_inputs_warp(P, b, nullptr, unused);
-    if (tid == 0) *rc = row_config_from(P, in);
-  }
+  // the row's options are asked for first and looked at once the sample has come in: one wait for both
+  const uint32_t word = tid < 32 ? row_inputs_word(P, b, nullptr) : 0u;
   const unsigned char* row = reinterpret_cast<const unsigned char*>(P.logits) + (size_t)b * P.row_stride * (16 / T::PER_VEC);
   const int vecs = sample_vecs(P.vocab, T::PER_VEC);
-  sample_maxima<T>(row, P.vocab, vecs, runs, sorted, P.rows >= SAMPLE_SIDE_BY_SIDE_ROWS);
+  sample_maxima<T>(row, P.vocab, vecs, runs, sorted, P.rows >= SAMPLE_SIDE_BY_SIDE_ROWS, [&]() {
+    if (tid < 32) {
+      uint32_t unused;
+      const RowIn in = row_inputs_from(P, word, unused);
+      if (tid == 0) *rc = row_config_from(P, in);
+    }
+  });
   const float floor_l = floor_from_sample(*rc, P.vocab, SAMPLE_CHUNKS * vecs * T::PER_VEC, P.list_cap, sorted, P.softcap > 0.0f);
   if (tid == 0)
     P.list_info[b] = INFO_READY | (lean_takes(P, *rc, floor_l) ? INFO_LEAN : 0ull) | (unsigned long long)__float_as_uint(floor_l);

@@ -199,7 +199,7 @@ __device__ inline RowIn row_inputs(const KParams& P, int b) {
 // The same inputs, fetched by a whole warp at once: every word comes from a lane of its own, so
 // the loads overlap instead of following one another.  `extra` (may be null) is one more word to
 // fetch alongside; it comes back in extra_out.
-__device__ inline RowIn row_inputs_warp(const KParams& P, int b, const void* extra, uint32_t& extra_out) {
+__device__ inline uint32_t row_inputs_word(const KParams& P, int b, const void* extra) {
   const int lane = threadIdx.x & 31;
   const uint32_t* src = nullptr;
   if (lane < 5) {
@@ -219,7 +219,11 @@ __device__ inline RowIn row_inputs_warp(const KParams& P, int b, const void* ext
     src = reinterpret_cast<const uint32_t*>(extra);
   }
   // (the extra word is another kernel's output: read past L1)
-  const uint32_t w = src ? (lane == 11 ? __ldcg(src) : *src) : 0u;
+  return src ? (lane == 11 ? __ldcg(src) : *src) : 0u;
+}
+// ... and handed round: `w` is what row_inputs_word() gave this lane (a caller with other loads to
+// issue puts them between the two, so that one wait covers both)
+__device__ inline RowIn row_inputs_from(const KParams& P, uint32_t w, uint32_t& extra_out) {
   uint32_t v[12];
 #pragma unroll
   for (int i = 0; i < 12; ++i) v[i] = __shfl_sync(FULL, w, i);
@@ -239,6 +243,9 @@ __device__ inline RowIn row_inputs_warp(const KParams& P, int b, const void* ext
   in.pos = P.position ? (int)v[10] : P.position_scalar;
   extra_out = v[11];
   return in;
+}
+__device__ inline RowIn row_inputs_warp(const KParams& P, int b, const void* extra, uint32_t& extra_out) {
+  return row_inputs_from(P, row_inputs_word(P, b, extra), extra_out);
 }
 
 __device__ inline RowCfg row_config_from(const KParams& P, const RowIn& in) {
