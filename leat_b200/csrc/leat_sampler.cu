@@ -514,7 +514,7 @@ int leat_argmax(leat_sampler_t* h, const float* x, int32_t rows, int32_t vocab, 
   if (rc != LEAT_OK) return rc;
   if (!out) return LEAT_E_ARGUMENT;
   P.force_greedy = 1;
-  if (pick_vec(P) == 4 && vocab >= kArgmaxMinVocab && !h->tune_no_filter) {
+  if (pick_vec(P) == 4 && vocab >= kArgmaxMinVocab && rows <= 65535 && !h->tune_no_filter) {
     // rows of whole aligned vectors: one launch of a kernel of its own
     h->launches = 0;
     if (rows == 0) return LEAT_OK;
