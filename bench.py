@@ -334,10 +334,11 @@ def run_one(args) -> None:
     w = workloads.CONFIGS[args.workload](**kw)
     sampler = Sampler(max(w.rows, 8), w.vocab, 256, device)
     dw = DeviceWorkload(w, device, min_pool_bytes=0, max_copies=1)
+    step = (lambda i: sampler.argmax(dw.pool[0])) if args.op == "argmax" else (lambda i: dw.step(sampler, i))
     for i in range(args.warmup):
-        dw.step(sampler, i)
-    total, _ = timed_replays(lambda i: dw.step(sampler, i), args.steps)
-    print(json.dumps({"workload": WORKLOAD_NAMES[args.workload], "rows": w.rows, "vocab": w.vocab,
+        step(i)
+    total, _ = timed_replays(step, args.steps)
+    print(json.dumps({"workload": WORKLOAD_NAMES[args.workload], "op": args.op, "rows": w.rows, "vocab": w.vocab,
                       "ms_per_step": total / args.steps,
                       "launch": dict(zip(("threads", "slices", "shared_bytes"),
                                          sampler.plan(w.rows, w.vocab, 0 if w.history is None else w.history.shape[1]))),
@@ -604,6 +605,8 @@ def main() -> None:
     parser.add_argument("--workload", type=int, default=0, choices=[0, 1, 2, 3, 4, 5],
                         help="profiling aid: time only this configuration, launched from Python, and print a short line")
     parser.add_argument("--rows", type=int, default=0, help="with --workload: fewer rows than the configuration has")
+    parser.add_argument("--op", default="sample", choices=["sample", "argmax"],
+                        help="with --workload: the sampler's step (default) or ops.argmax over the same logits")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
     args.steps = max(args.steps, 1)
